@@ -1,0 +1,61 @@
+// Shared helpers for the sm_100a kernels of this engine.
+//
+// Every launcher is an extern "C" function over raw device pointers and a
+// stream; it returns 0 on success or a negative code for a refused argument
+// (see SB_ERR_*), or the positive cudaError_t of a failed launch. Activations
+// and weights are float (dtype code 0) or __nv_bfloat16 (dtype code 1); the
+// residual stream, softmax statistics, norms, rotation angles and logits are
+// float in both modes.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SB_DTYPE_F32 0
+#define SB_DTYPE_BF16 1
+
+#define SB_ERR_DTYPE (-1)      // unsupported dtype code
+#define SB_ERR_SHAPE (-2)      // a size the kernel refuses
+#define SB_ERR_ALIGN (-3)      // a pointer or stride not aligned as the kernel needs
+#define SB_ERR_LIMIT (-4)      // a size beyond a stated maximum
+
+#define SB_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define SB_LAUNCH_CHECK()                      \
+  do {                                         \
+    cudaError_t e_ = cudaGetLastError();       \
+    if (e_ != cudaSuccess) return (int)e_;     \
+  } while (0)
+
+namespace sb {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// The order of additions depends only on blockDim, never on the batch.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = (lane < nwarps) ? smem32[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace sb

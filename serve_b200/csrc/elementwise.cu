@@ -1,0 +1,284 @@
+// Embedding gather, residual-add + RMSNorm, SwiGLU activation, rotary + cache
+// write, and sampling. All arithmetic is float; T is the storage type of
+// activations and weights.
+//
+// Formulas: serve/model.py:63-68 (RMSNorm), :85 (SwiGLU), :234-244 (rotation),
+// :120-124 (cache write), serve/run.py:47-60 (sampling).
+#include "common.cuh"
+
+using namespace sb;
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out,
+                                 int dim, int vocab) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  const T* src = table + (size_t)(ok ? tok : 0) * dim;
+  float* dst = out + (size_t)t * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ok ? to_float(src[i]) : 0.f;
+}
+
+SB_EXPORT int sb_embedding(const int* tokens, const void* table, float* out, int n_tokens, int dim, int vocab, int dtype,
+                           cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (dim <= 0 || vocab <= 0) return SB_ERR_SHAPE;
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (dtype == SB_DTYPE_F32)
+    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, dim, vocab);
+  else if (dtype == SB_DTYPE_BF16)
+    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, dim, vocab);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------- add + RMSNorm
+// One block per row. x (float residual) += delta if given (and is written back
+// when update_x); out = x * rsqrt(mean(x^2) + eps) * weight, rounded once.
+// With rows != nullptr, row b of the output comes from x[rows[b]] and x is not
+// written.
+template <typename T, typename W>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
+                                   const W* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+  __shared__ float red[32];
+  extern __shared__ float rowbuf[];  // dim floats
+  const int b = blockIdx.x;
+  const int src_row = rows ? rows[b] : b;
+  float* xr = x + (size_t)src_row * dim;
+  const T* dr = delta ? delta + (size_t)src_row * dim : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) v += to_float(dr[i]);
+    rowbuf[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  T* orow = out + (size_t)b * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = rowbuf[i];
+    if (!rows && dr) xr[i] = v;
+    orow[i] = from_float<T>(v * inv * to_float(weight[i]));
+  }
+}
+
+template <typename T>
+static int launch_add_rmsnorm(float* x, const void* delta, const int* rows, const void* weight, int weight_dtype, void* out,
+                              int n_rows, int dim, float eps, cudaStream_t stream) {
+  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  const size_t smem = (size_t)dim * sizeof(float);
+  if (smem > 200 * 1024) return SB_ERR_LIMIT;
+  if (weight_dtype == SB_DTYPE_F32) {
+    auto k = add_rmsnorm_kernel<T, float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, rows, (const float*)weight, (T*)out, dim, eps);
+  } else if (weight_dtype == SB_DTYPE_BF16) {
+    auto k = add_rmsnorm_kernel<T, __nv_bfloat16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, rows, (const __nv_bfloat16*)weight, (T*)out, dim, eps);
+  } else {
+    return SB_ERR_DTYPE;
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+SB_EXPORT int sb_add_rmsnorm(float* x, const void* delta, const int* rows, const void* weight, int weight_dtype, void* out,
+                             int n_rows, int dim, float eps, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0) return SB_ERR_SHAPE;
+  if (dtype == SB_DTYPE_F32) return launch_add_rmsnorm<float>(x, delta, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
+  if (dtype == SB_DTYPE_BF16)
+    return launch_add_rmsnorm<__nv_bfloat16>(x, delta, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
+  return SB_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// gate_up: [T, 2*I] (gate columns first, then up); out[t,i] = silu(gate)*up.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_float(gate_up[t * 2 * inter + i]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + i]);
+    const float s = g / (1.0f + expf(-g));
+    out[idx] = from_float<T>(s * u);
+  }
+}
+
+SB_EXPORT int sb_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (inter <= 0) return SB_ERR_SHAPE;
+  const size_t total = (size_t)n_tokens * inter;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == SB_DTYPE_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+  else if (dtype == SB_DTYPE_BF16)
+    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ------------------------------------------------------ rotary + cache write
+// qkv: [T, (H + 2*Hkv) * D]. Queries and keys are rotated (angle = position *
+// inv_freq[j], float); queries in place, rotated keys and plain values go to
+// the request's pages: cache[page, pos % ps, kv_head, :], page =
+// block_table[row, pos / ps]. pairing 0: pairs (j, j + rot/2); 1: (2j, 2j+1).
+// A page id < 0 or a block index beyond the table is counted in *errors and
+// the write is skipped.
+template <typename T>
+__global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ token_row,
+                                        const float* __restrict__ inv_freq, int pairing, int rot, int H, int Hkv, int D,
+                                        T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ block_table, int bt_width,
+                                        int ps, int num_pages, int write_cache, int* __restrict__ errors) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rot >> 1;
+  T* row = qkv + (size_t)t * (H + 2 * Hkv) * D;
+  size_t cache_base = 0;
+  bool cache_ok = false;
+  if (write_cache) {
+    const int blk = pos / ps;
+    const int r = token_row[t];
+    int page = (blk < bt_width && pos >= 0) ? block_table[(size_t)r * bt_width + blk] : -1;
+    cache_ok = page >= 0 && page < num_pages;
+    if (!cache_ok && threadIdx.x == 0) atomicAdd(errors, 1);
+    cache_base = ((size_t)(cache_ok ? page : 0) * ps + (pos % ps)) * Hkv * D;
+  }
+  // rotated pairs of q heads and k heads
+  const int n_rot_heads = H + Hkv;
+  for (int w = threadIdx.x; w < n_rot_heads * half; w += blockDim.x) {
+    const int h = w / half, j = w - h * half;
+    const float ang = (float)pos * inv_freq[j];
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    const int i0 = pairing == 0 ? j : 2 * j;
+    const int i1 = pairing == 0 ? j + half : 2 * j + 1;
+    T* hv = row + (size_t)h * D;
+    const float a = to_float(hv[i0]), b = to_float(hv[i1]);
+    const T o0 = from_float<T>(a * cs - b * sn);
+    const T o1 = from_float<T>(b * cs + a * sn);
+    if (h < H) {
+      hv[i0] = o0;
+      hv[i1] = o1;
+    } else if (cache_ok) {
+      T* dst = kc + cache_base + (size_t)(h - H) * D;
+      dst[i0] = o0;
+      dst[i1] = o1;
+    }
+  }
+  if (cache_ok) {
+    // key elements beyond the rotary width, and all value elements, are copied as they are
+    const int tail = D - rot;
+    for (int w = threadIdx.x; w < Hkv * tail; w += blockDim.x) {
+      const int h = w / tail, i = rot + (w - h * tail);
+      kc[cache_base + (size_t)h * D + i] = row[(size_t)(H + h) * D + i];
+    }
+    const T* vrow = row + (size_t)(H + Hkv) * D;
+    for (int w = threadIdx.x; w < Hkv * D; w += blockDim.x) vc[cache_base + w] = vrow[w];
+  }
+}
+
+SB_EXPORT int sb_rope_cache_write(void* qkv, const int* positions, const int* token_row, const float* inv_freq, int pairing,
+                                  int rot, int H, int Hkv, int D, void* kc, void* vc, const int* block_table, int bt_width,
+                                  int ps, int num_pages, int write_cache, int* errors, int n_tokens, int dtype,
+                                  cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || Hkv <= 0 || D <= 0 || rot < 0 || rot > D || (rot & 1) || ps <= 0) return SB_ERR_SHAPE;
+  const int threads = 128;
+  if (dtype == SB_DTYPE_F32)
+    rope_cache_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, positions, token_row, inv_freq, pairing, rot, H,
+                                                                     Hkv, D, (float*)kc, (float*)vc, block_table, bt_width, ps,
+                                                                     num_pages, write_cache, errors);
+  else if (dtype == SB_DTYPE_BF16)
+    rope_cache_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        (__nv_bfloat16*)qkv, positions, token_row, inv_freq, pairing, rot, H, Hkv, D, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc,
+        block_table, bt_width, ps, num_pages, write_cache, errors);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------- sampling
+// One block per row of float logits [L, V]. temperature 0: the largest logit,
+// lowest index on ties (serve/run.py:56-57). Otherwise the Gumbel-max form of
+// run.py:48-60: argmax_i softmax(l/T)_i / q_i with q ~ Exp(1), which is
+// argmax_i (l_i / T - log q_i). The uniform behind q_i comes from a counter
+// hash of (seed, request id, index of the token in its request, i), so a draw
+// does not depend on what else is in the batch.
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
+  return x;
+}
+
+__device__ __forceinline__ float counter_uniform(uint32_t seed_lo, uint32_t seed_hi, uint32_t req, uint32_t tok, uint32_t i) {
+  uint32_t h = mix32(seed_lo ^ 0x9E3779B9U);
+  h = mix32(h ^ seed_hi);
+  h = mix32(h + req * 0x85EBCA6BU);
+  h = mix32(h ^ (tok * 0xC2B2AE35U));
+  h = mix32(h + i);
+  return ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1)
+}
+
+__global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                              const int* __restrict__ req_ids, const int* __restrict__ tok_index, uint32_t seed_lo,
+                              uint32_t seed_hi, int vocab, int* __restrict__ out) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const int r = blockIdx.x;
+  const float* lr = logits + (size_t)r * vocab;
+  const float temp = temperature[r];
+  const uint32_t req = (uint32_t)req_ids[r], tok = (uint32_t)tok_index[r];
+  float best = -INFINITY;
+  int besti = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    float s = lr[i];
+    if (temp > 0.f) {
+      const float u = counter_uniform(seed_lo, seed_hi, req, tok, (uint32_t)i);
+      const float q = -logf(u);             // Exp(1)
+      s = s / temp - logf(q);
+    }
+    if (s > best || (s == best && i < besti)) { best = s; besti = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+    if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sval[warp] = best; sidx[warp] = besti; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = lane < nw ? sval[lane] : -INFINITY;
+    besti = lane < nw ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    }
+    if (lane == 0) out[r] = (besti == 0x7fffffff) ? 0 : besti;
+  }
+}
+
+SB_EXPORT int sb_sample(const float* logits, const float* temperature, const int* req_ids, const int* tok_index,
+                        unsigned long long seed, int n_rows, int vocab, int* out, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (vocab <= 0) return SB_ERR_SHAPE;
+  const int threads = vocab >= 4096 ? 1024 : 256;
+  sample_kernel<<<n_rows, threads, 0, stream>>>(logits, temperature, req_ids, tok_index, (uint32_t)(seed & 0xffffffffULL),
+                                                (uint32_t)(seed >> 32), vocab, out);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

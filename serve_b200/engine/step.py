@@ -1,0 +1,245 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes any mix of prompt portions and single decoded tokens, cut
+anywhere. It reserves cache pages for the new tokens, packs the batch into one
+int32 buffer (one host-to-device copy), runs the model on exactly the tokens it
+was given, against the cache earlier steps left, and returns float32 logits at
+the wanted places. The reference has two separate functions that cannot be
+mixed (serve/run.py:63-106) and whose prefill assumes position 0
+(serve/kernels/attn_prefill.py:116-134); this is the one function that
+replaces both.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)   # places among ``tokens`` whose logits are wanted
+
+
+@dataclass(frozen=True)
+class BatchShape:
+    """Host-side facts about a batch that kernels size their grids from."""
+
+    rows: int          # requests in the step
+    tokens: int        # tokens in the step
+    max_q: int         # most tokens any request brings
+    max_kv: int        # longest sequence after the step
+    pure_decode: bool  # every request brings exactly one token
+
+
+@dataclass
+class StepContext:
+    rt: object
+    shape: BatchShape
+    tokens: torch.Tensor        # [T] int32
+    positions: torch.Tensor     # [T] int32 absolute position of each token
+    token_row: torch.Tensor     # [T] int32 row (request index in the step) of each token
+    cu_q: torch.Tensor          # [R+1] int32 prefix sums of tokens per row
+    kv_len: torch.Tensor        # [R] int32 sequence length after this step
+    slots: torch.Tensor         # [R] int32 state slot of each row
+    logit_rows: torch.Tensor    # [L] int32 indices into the T tokens
+    block_tables: List[torch.Tensor]   # per cache group: [R, W] int32
+    rids: List[Hashable] = field(default_factory=list)
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class _Layout:
+    """Where each array of a step lies in the packed int32 buffer."""
+
+    def __init__(self, t: int, r: int, l: int, widths: Sequence[int]):
+        off = 0
+        self.spans: Dict[str, tuple] = {}
+        for name, n in (("tokens", t), ("positions", t), ("token_row", t), ("cu_q", r + 1), ("kv_len", r),
+                        ("slots", r), ("logit_rows", l)):
+            self.spans[name] = (off, n)
+            off += _align4(max(n, 1))
+        self.tables = []
+        for w in widths:
+            self.tables.append((off, r, w))
+            off += _align4(r * w)
+        self.total = off
+
+
+class Stepper:
+    def __init__(self, model, cache, runtime, max_tokens_per_step: int, use_cuda_graphs: bool = False):
+        self.model = model
+        self.cache = cache
+        self.rt = runtime
+        self.max_tokens_per_step = max_tokens_per_step
+        self.views = cache.views()
+        self.on_cuda = runtime.device.type == "cuda"
+        self.use_cuda_graphs = use_cuda_graphs and self.on_cuda
+        # two pinned staging buffers used in turn: one may still be in flight to the device
+        self._hosts: List[Optional[torch.Tensor]] = [None, None]
+        self._events: List[object] = [None, None]
+        self._turn = 0
+        self._dev: Optional[torch.Tensor] = None
+        self._graphs: Dict[int, object] = {}
+        self.launched_graphs = 0
+
+    # ---- buffers ----------------------------------------------------------
+    def _buffers(self, n: int):
+        self._turn ^= 1
+        i = self._turn
+        if self._dev is None or self._dev.numel() < n:
+            cap = 1 << (max(n, 4096) - 1).bit_length()
+            if self.on_cuda:
+                torch.cuda.current_stream(self.rt.device).synchronize()
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
+            self._hosts = [None, None]
+        if self._hosts[i] is None:
+            self._hosts[i] = torch.empty(self._dev.numel(), dtype=torch.int32, pin_memory=self.on_cuda)
+            self._events[i] = torch.cuda.Event() if self.on_cuda else None
+        elif self._events[i] is not None:
+            self._events[i].synchronize()   # the copy that last used this buffer has finished
+        return self._hosts[i], self._dev
+
+    # ---- the step -----------------------------------------------------------
+    def plan(self, entries: Sequence[StepEntry]):
+        """Validate a batch and reserve its pages (raises OutOfPages, changing nothing)."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        batch = []
+        total = 0
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.rid!r} brings no tokens")
+            for w in e.want:
+                if not (0 <= w < n):
+                    raise ValueError(f"request {e.rid!r} wants place {w} of {n} tokens")
+            total += n
+        if total > self.max_tokens_per_step:
+            raise ValueError(f"the step holds {total} tokens; the limit is {self.max_tokens_per_step}")
+        opened = []
+        try:
+            for e in entries:
+                if not self.cache.is_open(e.rid):
+                    self.cache.open(e.rid)
+                    opened.append(e.rid)
+                batch.append((e.rid, self.cache.length(e.rid) + len(e.tokens)))
+            self.cache.reserve(batch)
+        except Exception:
+            for rid in opened:
+                self.cache.close(rid)
+            raise
+        return batch
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch; returns [wanted, vocab] float32 logits (None if nothing is wanted)."""
+        batch = self.plan(entries)
+        r = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        starts = [self.cache.length(e.rid) for e in entries]
+        new_lens = [n for _, n in batch]
+        t = sum(q_lens)
+        n_want = sum(len(e.want) for e in entries)
+        pure_decode = all(q == 1 for q in q_lens)
+        graphable = self.use_cuda_graphs and pure_decode and n_want == r and r <= 512
+        rids = [e.rid for e in entries]
+        if graphable:
+            widths = [self.cache.max_blocks for _ in self.cache.groups]
+        else:
+            widths = [max(self.cache.blocks_for(n) for n in new_lens) for _ in self.cache.groups]
+        lay = _Layout(t, r, n_want, widths)
+        host, dev = self._buffers(lay.total)
+        h = host.numpy()
+        o, _ = lay.spans["tokens"]
+        pos_o, _ = lay.spans["positions"]
+        row_o, _ = lay.spans["token_row"]
+        cu_o, _ = lay.spans["cu_q"]
+        kv_o, _ = lay.spans["kv_len"]
+        sl_o, _ = lay.spans["slots"]
+        lr_o, _ = lay.spans["logit_rows"]
+        at = 0
+        li = 0
+        h[cu_o] = 0
+        for i, e in enumerate(entries):
+            n = q_lens[i]
+            h[o + at: o + at + n] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
+            h[pos_o + at: pos_o + at + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+            h[row_o + at: row_o + at + n] = i
+            for w in e.want:
+                h[lr_o + li] = at + w
+                li += 1
+            at += n
+            h[cu_o + i + 1] = at
+            h[kv_o + i] = new_lens[i]
+            h[sl_o + i] = self.cache.slot(e.rid)
+        for gi, (off, rr, w) in enumerate(lay.tables):
+            rows = self.cache.table_rows(gi, rids, w)
+            h[off: off + rr * w] = rows.reshape(-1)
+        dev[: lay.total].copy_(host[: lay.total], non_blocking=True)
+        if self._events[self._turn] is not None:
+            self._events[self._turn].record()
+
+        def view(name):
+            off, n = lay.spans[name]
+            return dev[off: off + n]
+
+        ctx = StepContext(
+            rt=self.rt,
+            shape=BatchShape(r, t, max(q_lens), max(new_lens), pure_decode),
+            tokens=view("tokens"), positions=view("positions"), token_row=view("token_row"),
+            cu_q=view("cu_q"), kv_len=view("kv_len"), slots=view("slots"), logit_rows=view("logit_rows"),
+            block_tables=[dev[off: off + rr * w].view(rr, w) for off, rr, w in lay.tables],
+            rids=rids,
+        )
+        if graphable:
+            logits = self._run_graph(ctx, r)
+        else:
+            logits = self.model.forward(ctx, self.views)
+        for rid, n in batch:
+            self.cache.commit(rid, n)
+        return logits
+
+    # ---- CUDA graphs for pure-decode steps ------------------------------------
+    def _run_graph(self, ctx: StepContext, r: int):
+        """Replay (capturing on first use) the decode step for ``r`` requests.
+
+        The packed buffer has the same layout and address for a given r, grids
+        are sized from the context limit rather than from this batch's lengths,
+        so one captured graph serves every decode step of that batch size.
+        """
+        g = self._graphs.get(r)
+        if g is None:
+            shape = BatchShape(r, r, 1, self.cache.max_context, True)
+            static_ctx = StepContext(**{**ctx.__dict__, "shape": shape})
+            # warm up outside capture (allocator pools, cuBLAS workspaces, lazy module loads)
+            s = torch.cuda.Stream(device=self.rt.device)
+            s.wait_stream(torch.cuda.current_stream(self.rt.device))
+            with torch.cuda.stream(s):
+                self.model.forward(static_ctx, self.views)
+            torch.cuda.current_stream(self.rt.device).wait_stream(s)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.model.forward(static_ctx, self.views)
+            g = (graph, out, self._dev)
+            self._graphs[r] = g
+        graph, out, dev = g
+        if dev is not self._dev:
+            # the packed buffer was re-made larger since capture: capture again
+            del self._graphs[r]
+            return self._run_graph(ctx, r)
+        graph.replay()
+        self.launched_graphs += 1
+        return out
+
+    def drop_graphs(self) -> None:
+        self._graphs.clear()

@@ -1,0 +1,177 @@
+"""The engine's kernels as Python calls over torch tensors (ctypes into the built libraries).
+
+There is no fallback: if a library cannot be built or loaded, or a kernel
+refuses a size, the call raises. Calls launch on torch's current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_ERRORS = {
+    -1: "unsupported dtype",
+    -2: "a size the kernel refuses",
+    -3: "a pointer or stride is not aligned as the kernel needs",
+    -4: "a size beyond the kernel's stated maximum",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc in _ERRORS:
+        raise KernelError(f"{what}: {_ERRORS[rc]}")
+    if rc < 0:
+        raise KernelError(f"{what}: library error {rc}")
+    raise KernelError(f"{what}: CUDA error {rc} at launch")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def core_jobs():
+    return [
+        {"name": "sb_core", "sources": ["elementwise.cu"]},
+        {"name": "sb_gemm", "sources": ["gemm_cublas.cu"], "libs": ["cublas"]},
+    ]
+
+
+def attention_job(head_dim: int):
+    return {"name": f"sb_attention_hd{head_dim}", "sources": ["attention_simt.cu"], "defines": [f"SB_HEAD_DIM={head_dim}"]}
+
+
+class CudaKernels:
+    """Loads (building if needed) the libraries and exposes one method per kernel."""
+
+    def __init__(self, device="cuda:0", head_dims=(), verbose: bool = True):
+        self.device = torch.device(device)
+        jobs = core_jobs() + [attention_job(d) for d in sorted(set(head_dims))]
+        for j in jobs:
+            j["verbose"] = verbose
+        paths = build.build_many(jobs)
+        self.paths = dict(paths)
+        self._core = ctypes.CDLL(paths["sb_core"])
+        self._gemm = ctypes.CDLL(paths["sb_gemm"])
+        self._attn: Dict[int, ctypes.CDLL] = {}
+        for d in set(head_dims):
+            self._attn[d] = ctypes.CDLL(paths[f"sb_attention_hd{d}"])
+        self._verbose = verbose
+        self._errors: Optional[torch.Tensor] = None
+        self.launches = 0
+
+    # ---- checks -----------------------------------------------------------
+    @staticmethod
+    def check_attention_shape(heads: int, kv_heads: int, head_dim: int) -> None:
+        if head_dim % 16 or not (16 <= head_dim <= 256):
+            raise KernelError(f"head_dim {head_dim} is not supported: the attention kernels take multiples of 16 from 16 to 256")
+        if heads % kv_heads:
+            raise KernelError(f"heads {heads} is not a multiple of kv_heads {kv_heads}")
+        if heads > 65535:
+            raise KernelError("more than 65535 heads")
+
+    def _attention_lib(self, head_dim: int):
+        lib = self._attn.get(head_dim)
+        if lib is None:
+            self.check_attention_shape(1, 1, head_dim)
+            job = attention_job(head_dim)
+            job["verbose"] = self._verbose
+            path = build.build_library(**job)
+            self.paths[job["name"]] = path
+            lib = self._attn[head_dim] = ctypes.CDLL(path)
+        return lib
+
+    def errors_tensor(self) -> torch.Tensor:
+        if self._errors is None:
+            self._errors = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._errors
+
+    def check_errors(self) -> None:
+        """Raise if a kernel met a page id or block index outside its table (synchronises)."""
+        if self._errors is not None:
+            n = int(self._errors.item())
+            if n:
+                self._errors.zero_()
+                raise KernelError(f"{n} cache writes met a missing page or a block index beyond the block table")
+
+    # ---- kernels ----------------------------------------------------------
+    def embedding(self, tokens, table, out) -> None:
+        self.launches += 1
+        _check(self._core.sb_embedding(_p(tokens), _p(table), _p(out), tokens.shape[0], table.shape[1], table.shape[0],
+                                       _DT[table.dtype], _stream()), "embedding")
+
+    def add_rmsnorm(self, x, delta, weight, eps, out) -> None:
+        self.launches += 1
+        _check(self._core.sb_add_rmsnorm(_p(x), _p(delta), _p(None), _p(weight), _DT[weight.dtype], _p(out), x.shape[0],
+                                         x.shape[1], ctypes.c_float(eps), _DT[out.dtype], _stream()), "add_rmsnorm")
+
+    def add_rmsnorm_rows(self, x, delta, rows, weight, eps, out) -> None:
+        self.launches += 1
+        _check(self._core.sb_add_rmsnorm(_p(x), _p(delta), _p(rows), _p(weight), _DT[weight.dtype], _p(out), rows.shape[0],
+                                         x.shape[1], ctypes.c_float(eps), _DT[out.dtype], _stream()), "add_rmsnorm_rows")
+
+    def linear(self, a, w, out) -> None:
+        """out[M,N] = a[M,K] @ w[N,K]^T (library matrix product)."""
+        if a.dtype != w.dtype or a.shape[1] != w.shape[1] or out.shape[0] != a.shape[0] or out.shape[1] != w.shape[0]:
+            raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} do not fit")
+        self.launches += 1
+        _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), a.shape[0], w.shape[0], a.shape[1], _DT[a.dtype], _DT[out.dtype],
+                                    _stream()), "linear")
+
+    def swiglu(self, gate_up, out) -> None:
+        self.launches += 1
+        _check(self._core.sb_swiglu(_p(gate_up), _p(out), out.shape[0], out.shape[1], _DT[out.dtype], _stream()), "swiglu")
+
+    def rope_cache_write(self, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
+                         k_cache, v_cache, block_table, page_size, write_cache) -> None:
+        self.launches += 1
+        num_pages = k_cache.shape[0] if k_cache is not None else 0
+        _check(self._core.sb_rope_cache_write(
+            _p(qkv), _p(positions), _p(token_row), _p(inv_freq), pairing, rotary_dim, heads, kv_heads, head_dim,
+            _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], page_size, num_pages,
+            1 if write_cache else 0, _p(self.errors_tensor()), qkv.shape[0], _DT[qkv.dtype], _stream()), "rope_cache_write")
+
+    def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
+                  page_size, scale, window, out, shape) -> None:
+        lib = self._attention_lib(head_dim)
+        self.launches += 1
+        _check(lib.sb_attention_simt(
+            _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
+            heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
+            _DT[qkv.dtype], _stream()), "attention")
+
+    def sample(self, logits, temperature, req_ids, tok_index, seed, out) -> None:
+        self.launches += 1
+        _check(self._core.sb_sample(_p(logits), _p(temperature), _p(req_ids), _p(tok_index), ctypes.c_ulonglong(seed),
+                                    logits.shape[0], logits.shape[1], _p(out), _stream()), "sample")
+
+
+_INSTANCES: Dict[str, CudaKernels] = {}
+
+
+def load_kernels(device="cuda:0", head_dims=(), verbose: bool = True) -> CudaKernels:
+    """The kernels for ``device`` (one object per device; more head sizes are built when first used)."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is available: this engine has no CPU path")
+    key = str(torch.device(device))
+    k = _INSTANCES.get(key)
+    if k is None:
+        k = _INSTANCES[key] = CudaKernels(device, head_dims, verbose)
+    else:
+        for d in head_dims:
+            k._attention_lib(d)
+    return k

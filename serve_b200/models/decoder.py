@@ -1,0 +1,76 @@
+"""A decoder built from a ``ModelSpec``: embedding, scheduled layers, final norm, head.
+
+It owns the parts and runs them in the order the schedule gives; it knows no
+architecture. The forward pass handles whatever tokens the step brings (flat
+[T]), reads and writes the cache through the views it is handed, and returns
+float32 logits for the requested rows only (the reference projects the last
+row of each prompt, serve/model.py:230-231, or every decode row, 226-227).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+from ..config.spec import ModelSpec, PartSpec
+from ..parts.base import CacheNeed, TensorDecl, build_part
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, runtime):
+        spec.validate()
+        self.spec = spec
+        self.rt = runtime
+        self.embedding = build_part("embedding", spec.embedding, runtime)
+        self.blocks = [build_part("block", PartSpec(ls.block), runtime, layer_spec=ls) for ls in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, runtime)
+        self.head = build_part("head", spec.head, runtime)
+        self.schedule = list(spec.schedule)
+
+    # ---- weights -------------------------------------------------------
+    def all_parts(self):
+        parts = [self.embedding]
+        for b in self.blocks:
+            parts.extend(b.parts())
+        parts.extend([self.final_norm, self.head])
+        return parts
+
+    def tensor_decls(self) -> Dict[str, TensorDecl]:
+        decls: Dict[str, TensorDecl] = {}
+        for part in self.all_parts():
+            for d in part.tensor_decls():
+                if d.name in decls and decls[d.name].shape != d.shape:
+                    raise ValueError(f"tensor {d.name} declared with shapes {decls[d.name].shape} and {d.shape}")
+                decls.setdefault(d.name, d)
+        return decls
+
+    def ignorable_tensors(self) -> List[str]:
+        names: List[str] = []
+        for part in self.all_parts():
+            names.extend(part.ignorable_tensors())
+        return names
+
+    def load(self, tensors) -> None:
+        for part in self.all_parts():
+            part.load(tensors)
+
+    # ---- cache ---------------------------------------------------------
+    def cache_needs(self) -> List[Optional[CacheNeed]]:
+        """One entry per schedule entry that owns a cache (None: that execution needs none)."""
+        needs: List[Optional[CacheNeed]] = []
+        for e in self.schedule:
+            if e.cache_of is not None:
+                needs.append(None)
+            else:
+                needs.append(self.blocks[e.layer].mixer.cache_need())
+        return needs
+
+    # ---- forward -------------------------------------------------------
+    def forward(self, ctx, cache_views):
+        """ctx: StepContext. cache_views[i]: CacheView of schedule entry i (or None)."""
+        x = self.embedding.forward(ctx.tokens, ctx)
+        pending = None
+        for i, e in enumerate(self.schedule):
+            x, pending = self.blocks[e.layer].forward(x, pending, ctx, cache_views[i])
+        if ctx.logit_rows.shape[0] == 0:
+            return None
+        h = self.final_norm.forward_rows(x, pending, ctx.logit_rows, ctx)
+        return self.head.forward(h, ctx)

@@ -1,0 +1,50 @@
+"""Dense gated feed-forward (SwiGLU): down( silu(gate x) * (up x) ).
+
+Reference: serve/model.py:80-85 (w1 = gate, w3 = up, w2 = down, no biases).
+Gate and up weights are fused at load into one [2*I, hidden] matrix so that one
+matrix product feeds the activation kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import FeedForward, TensorDecl, register_part
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    """params: hidden, intermediate, names (gate/up/down tensor names relative to prefix)."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden"])
+        self.intermediate = int(p["intermediate"])
+        names = p.get("names", {})
+        self.gate_name = self.prefix + names.get("gate", "gate_proj.weight")
+        self.up_name = self.prefix + names.get("up", "up_proj.weight")
+        self.down_name = self.prefix + names.get("down", "down_proj.weight")
+        self.w_gate_up = None
+        self.w_down = None
+
+    def tensor_decls(self):
+        return [
+            TensorDecl(self.gate_name, (self.intermediate, self.hidden)),
+            TensorDecl(self.up_name, (self.intermediate, self.hidden)),
+            TensorDecl(self.down_name, (self.hidden, self.intermediate)),
+        ]
+
+    def load(self, tensors):
+        self.w_gate_up = torch.cat([tensors[self.gate_name], tensors[self.up_name]], dim=0).contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+
+    def forward(self, h, ctx):
+        rt = self.rt
+        t = h.shape[0]
+        gate_up = rt.empty_act((t, 2 * self.intermediate))
+        rt.kernels.linear(h, self.w_gate_up, gate_up)
+        act = rt.empty_act((t, self.intermediate))
+        rt.kernels.swiglu(gate_up, act)
+        out = rt.empty_act((t, self.hidden))
+        rt.kernels.linear(act, self.w_down, out)
+        return out
