@@ -55,6 +55,14 @@ def attention_job(head_dim: int):
     return {"name": f"sb_attention_hd{head_dim}", "sources": ["attention_simt.cu"], "defines": [f"SB_HEAD_DIM={head_dim}"]}
 
 
+SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
+
+
+def all_jobs():
+    """Every library the engine can ask for (the build check compiles them all)."""
+    return core_jobs() + [attention_job(d) for d in SUPPORTED_HEAD_DIMS]
+
+
 class CudaKernels:
     """Loads (building if needed) the libraries and exposes one method per kernel."""
 
