@@ -10,4 +10,6 @@ from . import models, parts  # noqa: F401  (register architectures and parts)
 from .config import EngineConfig, LlamaConfig, load_config, load_preset  # noqa: F401
 from .engine import Engine, StepEntry  # noqa: F401
 
+from .run import Request, generate, load_model  # noqa: F401,E402
+
 __version__ = "0.1.0"

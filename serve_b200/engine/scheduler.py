@@ -1,0 +1,225 @@
+"""The scheduler: which requests run in the next step, and with how many tokens.
+
+The reference admits whole prompts first-come-first-served under a 2048-token
+budget and a reservation of prompt + max_new tokens against 90 % of the pool,
+and runs either a prefill step or a decode step, never both
+(serve/run.py:265-293). Here every step is mixed: each decoding request gets
+its one token first, what is left of the token budget goes to prompt portions
+(of running requests first, then of newly admitted ones, in arrival order), so
+a prompt may take several steps.
+
+When pages run out. With ``reserve_full`` admission promises prompt + max_new
+tokens to every request, as the reference does, and pages cannot run out.
+Without it, a step that cannot get its pages evicts the request admitted last:
+its pages and slot are given back, it returns to the head of the waiting queue
+and is later recomputed from its prompt plus the tokens it had generated. A
+request that could never fit the pool alone is refused when it is added.
+
+This module decides; it runs nothing. ``plan`` returns the step's entries and
+``update`` takes the sampled tokens. It needs the cache manager only for
+counting pages and slots.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence
+
+
+@dataclass
+class SchedRequest:
+    rid: int
+    prompt: List[int]
+    max_new_tokens: int
+    temperature: float = 0.0
+    stop_ids: Sequence[int] = ()
+    generated: List[int] = field(default_factory=list)
+    fed: int = 0                 # tokens of prompt+generated already in the cache
+    finished: bool = False
+    finish_reason: Optional[str] = None
+    preemptions: int = 0
+    last_logits: object = None
+
+    @property
+    def sequence_length(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    def pending(self) -> List[int]:
+        if self.fed >= len(self.prompt):
+            return self.generated[self.fed - len(self.prompt):]
+        return self.prompt[self.fed:] + self.generated
+
+
+@dataclass
+class PlannedEntry:
+    request: SchedRequest
+    tokens: List[int]
+    samples: bool                # the portion reaches the end of the sequence: a token is sampled from its last place
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    preemptions: int = 0
+    max_running: int = 0
+
+
+class Scheduler:
+    def __init__(self, cache, max_tokens_per_step: int, prefill_chunk: Optional[int] = None, reserve_full: bool = False,
+                 admission_fraction: float = 0.9, max_context: Optional[int] = None):
+        self.cache = cache
+        self.budget = max_tokens_per_step
+        self.prefill_chunk = prefill_chunk or max_tokens_per_step
+        self.reserve_full = reserve_full
+        self.admission_fraction = admission_fraction
+        self.max_context = max_context or cache.max_context
+        self.waiting: Deque[SchedRequest] = deque()
+        self.running: List[SchedRequest] = []     # in order of admission
+        self.finished: List[SchedRequest] = []
+        self.promised_pages = 0                   # reserve_full: pages promised to running requests
+        self.stats = SchedulerStats()
+        self.evicted: List[SchedRequest] = []     # evicted by the last plan(); the caller gives back their cache
+
+    # ---- sizes --------------------------------------------------------------
+    def _pool_pages(self) -> int:
+        return min(g.pool.num_pages for g in self.cache.groups) if self.cache.groups else 1 << 30
+
+    def _free_pages(self) -> int:
+        return min(g.pool.available for g in self.cache.groups) if self.cache.groups else 1 << 30
+
+    def _pages(self, tokens: int) -> int:
+        return self.cache.blocks_for(tokens)
+
+    # ---- requests -----------------------------------------------------------
+    def add(self, req: SchedRequest) -> None:
+        if len(req.prompt) == 0:
+            raise ValueError(f"request {req.rid}: empty prompt")
+        if req.max_new_tokens < 1:
+            raise ValueError(f"request {req.rid}: max_new_tokens must be at least 1")
+        # the last generated token is never fed back, so the cache holds at most prompt + max_new - 1 tokens
+        most = len(req.prompt) + req.max_new_tokens - 1
+        if most > self.max_context:
+            raise ValueError(f"request {req.rid}: prompt of {len(req.prompt)} + {req.max_new_tokens} new tokens exceeds the "
+                             f"context limit of {self.max_context}")
+        if self._pages(most) > self._pool_pages():
+            raise ValueError(f"request {req.rid}: needs {self._pages(most)} cache pages, the pool has {self._pool_pages()}")
+        self.waiting.append(req)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- planning -----------------------------------------------------------
+    def plan(self) -> List[PlannedEntry]:
+        """Entries of the next step. Evicts running requests if their pages cannot be had
+        (they are listed in ``self.evicted`` for the caller to close in the cache)."""
+        self.evicted = []
+        while True:
+            entries = self._plan_running()
+            need = self._new_pages(entries)
+            if need <= self._free_pages() + self._pages_of(self.evicted):
+                break
+            # pages ran out: the request admitted last goes back to the head of the queue
+            victim = self.running.pop()
+            self._evict(victim)
+        free_after = self._free_pages() + self._pages_of(self.evicted) - need
+        used = sum(len(e.tokens) for e in entries)
+        entries.extend(self._admit(self.budget - used, free_after))
+        self.stats.max_running = max(self.stats.max_running, len(self.running))
+        return entries
+
+    def _pages_of(self, reqs: Sequence[SchedRequest]) -> int:
+        return sum(self._pages(self.cache.length(r.rid)) if self.cache.is_open(r.rid) else 0 for r in reqs)
+
+    def _evict(self, victim: SchedRequest) -> None:
+        victim.fed = 0
+        victim.preemptions += 1
+        self.stats.preemptions += 1
+        if self.reserve_full:
+            self.promised_pages -= self._pages(len(victim.prompt) + victim.max_new_tokens - 1)
+        self.evicted.append(victim)
+        self.waiting.appendleft(victim)
+
+    def _plan_running(self) -> List[PlannedEntry]:
+        entries: List[PlannedEntry] = []
+        left = self.budget
+        # decoding requests first: one token each
+        for r in self.running:
+            if r.sequence_length - r.fed == 1 and left > 0:
+                entries.append(PlannedEntry(r, r.pending(), True))
+                left -= 1
+        # then portions of prompts already under way
+        for r in self.running:
+            n = r.sequence_length - r.fed
+            if n > 1 and left > 0:
+                take = min(n, self.prefill_chunk, left)
+                entries.append(PlannedEntry(r, r.pending()[:take], take == n))
+                left -= take
+        return entries
+
+    def _new_pages(self, entries: Sequence[PlannedEntry]) -> int:
+        need = 0
+        for e in entries:
+            r = e.request
+            have = self._pages(r.fed) if self.cache.is_open(r.rid) else 0
+            need += self._pages(r.fed + len(e.tokens)) - have
+        return need
+
+    def _admit(self, left: int, free_pages: int) -> List[PlannedEntry]:
+        entries: List[PlannedEntry] = []
+        free_slots = self.cache.free_slots + len(self.evicted)
+        while self.waiting and left > 0 and free_slots > 0:
+            r = self.waiting[0]
+            if r in self.evicted:
+                break   # evicted in this very step; it waits for the next
+            n = r.sequence_length - r.fed
+            take = min(n, self.prefill_chunk, left)
+            pages = self._pages(take)
+            if self.reserve_full:
+                promise = self._pages(len(r.prompt) + r.max_new_tokens - 1)
+                if self.promised_pages + promise > self.admission_fraction * self._pool_pages() and self.running:
+                    break
+                if pages > free_pages:
+                    break
+                self.promised_pages += promise
+            elif pages > free_pages:
+                break
+            self.waiting.popleft()
+            self.running.append(r)
+            entries.append(PlannedEntry(r, r.pending()[:take], take == n))
+            left -= take
+            free_pages -= pages
+            free_slots -= 1
+        return entries
+
+    # ---- after the step -----------------------------------------------------
+    def update(self, entries: Sequence[PlannedEntry], sampled: Sequence[int]) -> List[SchedRequest]:
+        """Account a finished step. ``sampled``: one token for each entry with ``samples`` set, in order.
+        Returns the requests that finished (the caller gives back their cache)."""
+        self.stats.steps += 1
+        done: List[SchedRequest] = []
+        it = iter(sampled)
+        for e in entries:
+            r = e.request
+            if r.fed + len(e.tokens) > len(r.prompt) and len(e.tokens) == 1:
+                self.stats.decode_tokens += 1
+            else:
+                self.stats.prefill_tokens += len(e.tokens)
+            r.fed += len(e.tokens)
+            if not e.samples:
+                continue
+            tok = int(next(it))
+            r.generated.append(tok)
+            if len(r.generated) >= r.max_new_tokens:
+                r.finished, r.finish_reason = True, "length"
+            elif tok in r.stop_ids:
+                r.finished, r.finish_reason = True, "stop"
+            if r.finished:
+                done.append(r)
+        for r in done:
+            self.running.remove(r)
+            self.finished.append(r)
+            if self.reserve_full:
+                self.promised_pages -= self._pages(len(r.prompt) + r.max_new_tokens - 1)
+        return done

@@ -88,3 +88,43 @@ def test_schedule_repeats_a_layer_and_shares_a_cache(tmp_path):
     got = helpers.replay(eng, helpers.trace_portions({"s": toks}, sizes=(11, 2, 7, 25)))
     helpers.compare_with_plain(got, plain, atol=2e-5)
     assert sum(v is not None and v.writes for v in eng.stepper.views) == 3
+
+
+# ---- generation through the entry point (scheduler + sampler + step), still with stand-in kernels ----
+def _plain_generate(w, cfg, prompt, n_new, temperature=0.0, seed=0, rid=0):
+    from tests.plain.llama_plain import sample_token
+
+    toks = list(prompt)
+    for i in range(n_new):
+        logits = llama_forward(w, cfg, toks)[-1]
+        toks.append(sample_token(logits, temperature, seed, rid, i))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name,temperature", [("a", 0.0), ("b", 0.8)])
+def test_generate_equals_plain_under_chunking_and_eviction(tmp_path, name, temperature):
+    from serve_b200.run import Request, generate
+
+    folder = helpers.make_folder(str(tmp_path / name), name, seed=3, std=0.08)
+    cfg, w = helpers.read_folder(folder)
+    lengths = [5, 9, 13] if name == "a" else [1, 17, 40, 70]
+    prompts = [helpers.random_tokens(cfg["vocab_size"], n, seed=20 + i) for i, n in enumerate(lengths)]
+    n_new = 8
+    want = [_plain_generate(w, cfg, p, n_new, temperature, seed=11, rid=i) for i, p in enumerate(prompts)]
+    page = 4 if name == "a" else 8
+    settings = [
+        dict(num_pages=64, max_tokens_per_step=256, prefill_chunk=None),       # whole prompts
+        dict(num_pages=64, max_tokens_per_step=24, prefill_chunk=16),          # portions of 16 mixed with decodes
+        dict(num_pages=-(-(max(lengths) + n_new) // page) + 3, max_tokens_per_step=32, prefill_chunk=16),  # pages run out
+    ]
+    for i, st in enumerate(settings):
+        ec = EngineConfig(dtype="float32", page_size=page, max_slots=4, max_context=128, device="cpu", use_cuda_graphs=False, **st)
+        eng = Engine.from_folder(folder, ec, kernels=EmuKernels())
+        reqs = [Request(torch.tensor(p), len(p), n_new) for p in prompts]
+        out = generate(eng, reqs, temperature=temperature, seed=11, return_logits=True)
+        assert [r.generated_tokens.tolist() for r in out] == want, f"setting {i}"
+        assert all(r.logits is not None and r.logits.shape == (cfg["vocab_size"],) for r in out)
+        if i == 2:
+            assert eng.last_stats.preemptions > 0, "this pool was meant to run out of pages"
+        assert eng.cache.live == 0
+        eng.cache.check()

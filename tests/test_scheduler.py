@@ -1,0 +1,119 @@
+"""The scheduler's decisions, with a stand-in for the step (no model): admission, portions under a
+token budget, mixing, finishing, and what happens when pages run out."""
+import pytest
+
+from serve_b200.cache import CacheManager
+from serve_b200.engine.scheduler import SchedRequest, Scheduler
+from serve_b200.parts import CacheNeed
+
+
+def _cache(num_pages, page=4, slots=8, ctx=512):
+    return CacheManager([CacheNeed(1, 16)], [None], page, num_pages, slots, ctx)
+
+
+def run(sched, cache, max_steps=10_000, token_of=lambda r: 7):
+    """Play the step function's part: reserve, commit, hand back a token per sampling entry."""
+    log = []
+    for _ in range(max_steps):
+        if not sched.has_work():
+            return log
+        planned = sched.plan()
+        for v in sched.evicted:
+            cache.close(v.rid)
+        assert planned, "nothing planned although there is work"
+        batch = []
+        for p in planned:
+            if not cache.is_open(p.request.rid):
+                cache.open(p.request.rid)
+            assert cache.length(p.request.rid) == p.request.fed
+            batch.append((p.request.rid, p.request.fed + len(p.tokens)))
+        cache.reserve(batch)          # must never raise: the scheduler counted the pages
+        for rid, n in batch:
+            cache.commit(rid, n)
+        cache.check()
+        log.append([(p.request.rid, len(p.tokens), p.samples) for p in planned])
+        done = sched.update(planned, [token_of(p.request) for p in planned if p.samples])
+        for r in done:
+            cache.close(r.rid)
+    raise AssertionError("the scheduler did not finish")
+
+
+def test_portions_under_a_token_budget_and_mixing():
+    cache = _cache(64)
+    s = Scheduler(cache, max_tokens_per_step=16, prefill_chunk=10)
+    s.add(SchedRequest(0, list(range(25)), 3))
+    s.add(SchedRequest(1, list(range(7)), 2))
+    log = run(s, cache)
+    assert log[0] == [(0, 10, False), (1, 6, False)]          # budget 16: 10 + 6
+    assert log[1] == [(1, 1, True), (0, 10, False)]            # single tokens first, then the next portion
+    flat = [e for step in log for e in step]
+    assert sum(n for rid, n, _ in flat if rid == 0) == 25 + 2  # prompt + fed-back tokens (the last is never fed)
+    assert all(sum(n for _, n, _ in step) <= 16 for step in log)
+    assert [len(r.generated) for r in sorted(s.finished, key=lambda r: r.rid)] == [3, 2]
+    # decode tokens come first in a step, beside portions of others
+    mixed = [step for step in log if any(n == 1 and smp for _, n, smp in step) and any(n > 1 for _, n, _ in step)]
+    assert mixed and all(step[0][1] == 1 for step in mixed)
+
+
+def test_first_come_first_served_and_slots():
+    cache = _cache(64, slots=2)
+    s = Scheduler(cache, max_tokens_per_step=64)
+    for i in range(4):
+        s.add(SchedRequest(i, [1] * 5, 2))
+    log = run(s, cache)
+    assert [rid for rid, _, _ in log[0]] == [0, 1]            # two slots
+    assert s.stats.max_running == 2
+    assert [r.rid for r in s.finished] == [0, 1, 2, 3]
+
+
+def test_finish_by_length_and_by_stop_id():
+    cache = _cache(64)
+    s = Scheduler(cache, 64)
+    s.add(SchedRequest(0, [1, 2, 3], 1))
+    s.add(SchedRequest(1, [1, 2, 3], 50, stop_ids=(9,)))
+    run(s, cache, token_of=lambda r: 9 if len(r.generated) == 4 else 5)
+    a, b = sorted(s.finished, key=lambda r: r.rid)
+    assert a.generated == [5] and a.finish_reason == "length"     # one token, from the prompt's last place, then freed
+    assert b.generated == [5, 5, 5, 5, 9] and b.finish_reason == "stop"
+    assert cache.live == 0
+
+
+def test_pages_run_out_evicts_the_last_admitted_and_recomputes():
+    cache = _cache(num_pages=6, page=4)                       # 24 tokens of cache
+    s = Scheduler(cache, max_tokens_per_step=32)
+    s.add(SchedRequest(0, [1] * 8, 12))                        # grows to 19 tokens: 5 pages
+    s.add(SchedRequest(1, [2] * 8, 12))
+    log = run(s, cache)
+    assert s.stats.preemptions >= 1
+    r0, r1 = sorted(s.finished, key=lambda r: r.rid)
+    assert len(r0.generated) == 12 and len(r1.generated) == 12
+    assert r0.preemptions == 0 and r1.preemptions >= 1        # the one admitted last gives way
+    # after eviction request 1 is recomputed from its prompt plus what it had generated
+    refeeds = [n for step in log for rid, n, _ in step if rid == 1 and n > 8]
+    assert refeeds, "the evicted request must come back with prompt + generated tokens"
+    assert cache.live == 0 and cache.groups[0].pool.in_use == 0
+
+
+def test_reserve_full_never_evicts():
+    cache = _cache(num_pages=10, page=4)
+    s = Scheduler(cache, max_tokens_per_step=32, reserve_full=True, admission_fraction=1.0)
+    for i in range(3):
+        s.add(SchedRequest(i, [1] * 8, 9))                    # 16 tokens -> 4 pages promised each
+    log = run(s, cache)
+    assert s.stats.preemptions == 0
+    assert [rid for rid, _, _ in log[0]] == [0, 1]            # the third would break the promise
+    assert s.promised_pages == 0
+
+
+def test_a_request_that_can_never_fit_is_refused():
+    cache = _cache(num_pages=3, page=4, ctx=64)
+    s = Scheduler(cache, 32)
+    with pytest.raises(ValueError, match="cache pages"):
+        s.add(SchedRequest(0, [1] * 10, 8))
+    with pytest.raises(ValueError, match="context limit"):
+        s.add(SchedRequest(1, [1] * 60, 8))
+    with pytest.raises(ValueError, match="empty prompt"):
+        s.add(SchedRequest(2, [], 8))
+    s.add(SchedRequest(3, [1] * 10, 3))                        # 12 tokens: exactly the pool
+    run(s, cache)
+    assert len(s.finished) == 1
