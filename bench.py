@@ -1,0 +1,261 @@
+"""Decode and prefill throughput of the engine at the Llama-3.2-1B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 (2,048-token prompts, context limit
+4,096), timed on the device with CUDA events over K decode steps after W warm-up steps; ``e2e`` is the same
+through the Python entry point ``serve_b200.generate`` with token ids coming from and going back to the host
+every step; ``prefill`` is one 2,048-token prompt; ``points`` holds decode at batch 1 and 64; ``roofline``
+compares the decode step with the bytes it has to read (every weight once, and the cache of the live requests).
+The weights (2.47 GB) are larger than the L2 cache, so no flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+PROMPT_LEN = 2048
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.path = None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    parts = [p.strip() for p in line.split(",")]
+                    if len(parts) >= 7 and parts[0].isdigit():
+                        rows.append(parts)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if rows:
+            sm = sorted(int(r[0]) for r in rows)
+            out["sm_mhz"] = sm[len(sm) // 2]
+            out["sm_max_mhz"] = int(rows[0][1])
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            out["reasons"] = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+            out["samples"] = len(rows)
+        return out
+
+
+def model_bytes_and_flops(cfg, dtype_bytes):
+    h, L, H, Hkv, D, I, V = (cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads, cfg.num_key_value_heads,
+                             cfg.head_dim, cfg.intermediate_size, cfg.vocab_size)
+    per_layer = (H + 2 * Hkv) * D * h + h * H * D + 2 * I * h + h * I
+    weights = (L * per_layer + V * h) * dtype_bytes                   # every weight a decode step uses, once
+    kv_per_token = L * 2 * Hkv * D * dtype_bytes
+    def prefill_flops(t):
+        return 2 * t * L * per_layer + L * 4 * D * H * t * (t + 1) // 2 + 2 * V * h
+    return weights, kv_per_token, prefill_flops
+
+
+def decode_bench(eng, sampler, batch, steps, warmup, vocab, seed):
+    """Prefill ``batch`` prompts of PROMPT_LEN tokens, then time ``steps`` decode steps on the device."""
+    import torch
+    from serve_b200.engine import StepEntry
+
+    g = torch.Generator().manual_seed(seed)
+    rids = [f"b{batch}-{i}" for i in range(batch)]
+    for rid in rids:
+        toks = torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist()
+        eng.step([StepEntry(rid, toks, [])])
+    feed = torch.randint(0, vocab, (warmup + steps, batch), generator=g).tolist()
+    temps, tok_idx = [0.0] * batch, [0] * batch
+
+    def one(i):
+        logits = eng.step([StepEntry(rid, [feed[i][j]], [0]) for j, rid in enumerate(rids)])
+        return sampler.sample(logits, temps, list(range(batch)), tok_idx)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    k = eng.kernels
+    l0, c0 = k.launches, k.library_calls
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / steps
+    ctx_mid = PROMPT_LEN + warmup + steps / 2.0
+    for rid in rids:
+        eng.end(rid)
+    return ms, ctx_mid, k.launches - l0, k.library_calls - c0
+
+
+def prefill_bench(eng, vocab, reps, seed):
+    import torch
+    from serve_b200.engine import StepEntry
+
+    g = torch.Generator().manual_seed(seed)
+    times = []
+    for i in range(reps + 2):
+        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        eng.step([StepEntry(f"p{i}", toks, [PREFILL_TOKENS - 1])])
+        ev1.record()
+        torch.cuda.synchronize()
+        eng.end(f"p{i}")
+        if i >= 2:
+            times.append(ev0.elapsed_time(ev1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def e2e_bench(eng, batch, steps, vocab, seed):
+    """Decoded tokens per second through serve_b200.generate: host token ids in, host token ids out, every step."""
+    import torch
+    from serve_b200 import Request, generate
+
+    g = torch.Generator().manual_seed(seed)
+    reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, steps + 4) for _ in range(batch)]
+    timeline = []
+    generate(eng, reqs, temperature=0.0, timeline=timeline)
+    dec = [(t, nd, b) for t, npf, nd, b in timeline if nd == batch and npf == 0]
+    # skip the first pure-decode steps (graph capture, warm-up); time from one step's end to the last step's end
+    skip = 3
+    if len(dec) <= skip + 1:
+        return None
+    t0, t1 = dec[skip][0], dec[-1][0]
+    n_steps = len(dec) - 1 - skip
+    return {"value": batch * n_steps / (t1 - t0), "unit": "tokens/s", "h2d_bytes_per_step": int(dec[-1][2]),
+            "d2h_bytes_per_step": 4 * batch, "steps": n_steps}
+
+
+def reference_arm(args):
+    print(json.dumps({"impl": "reference", "unavailable": "limei1221/serve is not installed under baseline/_ref on this box"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in the record)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import dataclasses
+
+    import torch
+
+    from serve_b200.config import EngineConfig, load_preset
+    from serve_b200.engine import Engine
+    from serve_b200.sampling import Sampler
+
+    cfg_full = load_preset("llama-3.2-1b")
+    cfg = cfg_full if args.layers is None else dataclasses.replace(cfg_full, num_hidden_layers=args.layers)
+    pk = peaks()
+    page = 64
+    max_batch = max(64, args.batch)
+    ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=max_batch * CONTEXT // page + 64, max_slots=max_batch + 2,
+                      max_tokens_per_step=max(PROMPT_LEN, PREFILL_TOKENS), max_context=CONTEXT)
+    with torch.inference_mode():
+        eng = Engine.from_config(cfg, seed=0, engine_config=ec)
+        sampler = Sampler(eng.kernels, eng.rt.device, seed=0)
+        weights, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, 2)
+
+        clocks = ClockSampler()
+        clocks.start()
+        ms, ctx_mid, launches, lib_calls = decode_bench(eng, sampler, args.batch, args.steps, args.warmup, cfg.vocab_size, seed=1)
+        clock_rec = clocks.stop()
+        value = args.batch * 1000.0 / ms
+        step_bytes = weights + args.batch * ctx_mid * kv_per_token
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+
+        points = {}
+        if not args.skip_points:
+            for b in (1, 64):
+                pms, _, _, _ = decode_bench(eng, sampler, b, max(16, args.steps // 2), args.warmup, cfg.vocab_size, seed=2 + b)
+                points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+
+        pre_ms = prefill_bench(eng, cfg.vocab_size, reps=5, seed=7)
+        pre_frac = prefill_flops(PREFILL_TOKENS) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+
+        e2e = e2e_bench(eng, args.batch, max(args.steps, 32), cfg.vocab_size, seed=9)
+
+    rec = {
+        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, 2048-token prompts, context 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform random token ids, seeded random weights N(0,0.02)",
+        "impl": "ours",
+        "config": {"model": "llama-3.2-1b-shape", "layers": cfg.num_hidden_layers, "layers_full": cfg_full.num_hidden_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": page,
+                   "parallelism": "single-gpu", "l2": "inputs larger than L2: 2.47 GB of weights read per step",
+                   "peaks": pk["source"]},
+        "e2e": e2e,
+        "gpu_launches": int(launches),
+        "library_gemm_calls": int(lib_calls),
+        "prefill": {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+                    "frac": round(pre_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_rec,
+    }
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -88,6 +88,7 @@ class Stepper:
         self._dev: Optional[torch.Tensor] = None
         self._graphs: Dict[int, object] = {}
         self.launched_graphs = 0
+        self.last_h2d_bytes = 0
 
     # ---- buffers ----------------------------------------------------------
     def _buffers(self, n: int):
@@ -186,6 +187,7 @@ class Stepper:
             rows = self.cache.table_rows(gi, rids, w)
             h[off: off + rr * w] = rows.reshape(-1)
         dev[: lay.total].copy_(host[: lay.total], non_blocking=True)
+        self.last_h2d_bytes = lay.total * 4
         if self._events[self._turn] is not None:
             self._events[self._turn].record()
 
@@ -228,17 +230,24 @@ class Stepper:
                 self.model.forward(static_ctx, self.views)
             torch.cuda.current_stream(self.rt.device).wait_stream(s)
             graph = torch.cuda.CUDAGraph()
+            k = self.rt.kernels
+            before = (getattr(k, "launches", 0), getattr(k, "library_calls", 0))
             with torch.cuda.graph(graph):
                 out = self.model.forward(static_ctx, self.views)
-            g = (graph, out, self._dev)
+            counts = (getattr(k, "launches", 0) - before[0], getattr(k, "library_calls", 0) - before[1])
+            g = (graph, out, self._dev, counts)
             self._graphs[r] = g
-        graph, out, dev = g
+        graph, out, dev, counts = g
         if dev is not self._dev:
             # the packed buffer was re-made larger since capture: capture again
             del self._graphs[r]
             return self._run_graph(ctx, r)
         graph.replay()
         self.launched_graphs += 1
+        k = self.rt.kernels
+        if hasattr(k, "launches"):
+            k.launches += counts[0]
+            k.library_calls += counts[1]
         return out
 
     def drop_graphs(self) -> None:

@@ -80,7 +80,8 @@ class CudaKernels:
             self._attn[d] = ctypes.CDLL(paths[f"sb_attention_hd{d}"])
         self._verbose = verbose
         self._errors: Optional[torch.Tensor] = None
-        self.launches = 0
+        self.launches = 0         # launches of this engine's own kernels
+        self.library_calls = 0    # library matrix products
 
     # ---- checks -----------------------------------------------------------
     @staticmethod
@@ -136,7 +137,7 @@ class CudaKernels:
         """out[M,N] = a[M,K] @ w[N,K]^T (library matrix product)."""
         if a.dtype != w.dtype or a.shape[1] != w.shape[1] or out.shape[0] != a.shape[0] or out.shape[1] != w.shape[0]:
             raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} do not fit")
-        self.launches += 1
+        self.library_calls += 1
         _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), a.shape[0], w.shape[0], a.shape[1], _DT[a.dtype], _DT[out.dtype],
                                     _stream()), "linear")
 

@@ -61,8 +61,13 @@ def load_model(model_name, device: str = "cuda", dtype=torch.bfloat16, **engine_
 
 @torch.inference_mode()
 def generate(model: Engine, requests: Sequence[Request], temperature: float = 0.0, return_logits: bool = False,
-             seed: int = 0, eos_token_id: Optional[int] = None) -> List[Request]:
-    """Run all requests to the end; token ids come from the host and go back to the host every step."""
+             seed: int = 0, eos_token_id: Optional[int] = None, timeline: Optional[list] = None) -> List[Request]:
+    """Run all requests to the end; token ids come from the host and go back to the host every step.
+
+    ``timeline``, if a list, receives one record per step after its tokens have reached the host:
+    (time.perf_counter(), prompt tokens in the step, decoded tokens in the step, bytes copied to the device)."""
+    import time
+
     ec = model.engine_config
     sched = Scheduler(model.cache, ec.max_tokens_per_step, ec.prefill_chunk, ec.reserve_full, ec.admission_fraction,
                       model.max_context)
@@ -87,6 +92,10 @@ def generate(model: Engine, requests: Sequence[Request], temperature: float = 0.
                                  [len(r.generated) for r in sampling])
             tokens = out.tolist()   # device -> host: the step's result
         done = sched.update(planned, tokens)
+        if timeline is not None:
+            n_dec = sum(1 for p in planned if len(p.tokens) == 1 and p.samples and p.request.generated and len(p.request.generated) > 1)
+            timeline.append((time.perf_counter(), sum(len(p.tokens) for p in planned) - n_dec, n_dec,
+                             model.stepper.last_h2d_bytes + 12 * len(sampling)))
         if done:
             rows = {id(r): i for i, r in enumerate(sampling)}
             for r in done:
