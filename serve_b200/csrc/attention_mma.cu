@@ -1,0 +1,406 @@
+// Paged causal attention for bfloat16 on the tensor cores (mma.sync m16n8k16, float accumulation),
+// one kernel for prompt portions and for decoded tokens.
+//
+// Work is cut per (request, kv head): the G = H / Hkv query heads that share a kv head are folded into the
+// row dimension, row m of a request's tile standing for (token m / G, head hk*G + m % G), so a key/value
+// tile is fetched once for the whole group. Two shapes of thread block exist:
+//   * "wide" (4 warps x 16 rows = 64 rows, every warp walks all keys of a 64-key tile): prompt portions;
+//   * "deep" (16 rows, the 4 warps split the keys of a tile, results merged through shared memory; the
+//     key range may also be split over several blocks whose partial results a second kernel merges):
+//     requests that bring at most 16 / G tokens, i.e. decoding.
+// A request is handled by the shape its row count fits; the other shape's blocks leave it alone.
+//
+// Scores, running maxima, sums and outputs are float; probabilities are rounded to bfloat16 for the
+// second product, as the reference does (serve/kernels/attn_prefill.py:71, attn_decode.py:110). The
+// recurrences are those of attn_prefill.py:58-72 with exp2 and a folded log2(e) (attn_prefill.py:330-331).
+// Compile with -DSB_HEAD_DIM=<multiple of 16, 16..256>.
+#include "common.cuh"
+
+#ifndef SB_HEAD_DIM
+#error "define SB_HEAD_DIM"
+#endif
+
+using namespace sb;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int D = SB_HEAD_DIM;
+constexpr int BN = 64;               // keys per tile
+constexpr int LDS = D + 8;           // row stride in shared memory (elements): 16 bytes of padding
+constexpr int THREADS = 128;
+constexpr int CHUNKS = D / 8;        // 16-byte pieces per row
+constexpr float LOG2E = 1.4426950408889634f;
+
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head_dim must be a multiple of 16 in 16..256");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;   // 0: nothing is read, the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Params {
+  const bf16* qkv; int q_stride;
+  const bf16* kc; const bf16* vc;
+  const int* block_table; int bt_width;
+  const int* cu_q; const int* kv_len;
+  int H, Hkv, G, ps, num_pages;
+  float scale_log2; int window;
+  bf16* out;
+  // deep shape only
+  int split_size, num_splits;
+  float* part_o;    // [R, Hkv, splits, 16, D]
+  float* part_ml;   // [R, Hkv, splits, 16, 2]
+};
+
+// Fetch keys [kt, kt+BN) of kv head hk into one stage of shared memory; keys outside [lo, hi) become zeros.
+__device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int hk, int kt, int lo, int hi, bf16* Ks, bf16* Vs) {
+#pragma unroll
+  for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += THREADS) {
+    const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
+    const int key = kt + row;
+    bool ok = key >= lo && key < hi;
+    size_t off = 0;
+    if (ok) {
+      const int blk = key / p.ps;
+      const int page = blk < p.bt_width ? bt[blk] : -1;
+      ok = page >= 0 && page < p.num_pages;
+      if (ok) off = (((size_t)page * p.ps + (key - blk * p.ps)) * p.Hkv + hk) * D + ch * 8;
+    }
+    cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
+    cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+  }
+}
+
+// WM warps along rows, WN warps along the keys of a tile (WM * WN == 4).
+template <int WM, int WN>
+__global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) {
+  constexpr int BM = WM * 16;
+  constexpr int KW = BN / WN;          // keys per warp per tile
+  constexpr int NT = KW / 8;           // score n-tiles per warp
+  constexpr bool DEEP = (WN > 1);
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [BM][LDS]
+  bf16* KVs = Qs + BM * LDS;                        // 2 stages x (K [BN][LDS], V [BN][LDS])
+
+  const int r = blockIdx.z, hk = blockIdx.y;
+  const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
+  const int G = p.G;
+  const int M = qn * G;                             // rows of this (request, kv head)
+  int m0, split;
+  if (DEEP) {
+    if (M > 16 || M <= 0) return;                   // the wide shape takes this request
+    m0 = 0; split = blockIdx.x;
+  } else {
+    if (M <= 16) return;                            // the deep shape takes this request
+    m0 = blockIdx.x * BM; split = 0;
+    if (m0 >= M) return;
+  }
+  const int L = p.kv_len[r];
+  const int p0 = L - qn;                            // position of the request's first query
+  const int tok_first = m0 / G, tok_last = min(m0 + BM, M) - 1;
+  int lo = p.window > 0 ? max(0, p0 + tok_first - p.window + 1) : 0;
+  int hi = p0 + tok_last / G + 1;                   // exclusive, <= L
+  if (DEEP) {
+    // this block's share of the keys
+    const int s_lo = split * p.split_size, s_hi = s_lo + p.split_size;
+    lo = max(lo, s_lo);
+    hi = min(hi, s_hi);
+  }
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = DEEP ? 0 : warp, wn = DEEP ? warp : 0;
+  const int g = lane >> 2, tq = lane & 3;
+  const int* bt = p.block_table + (size_t)r * p.bt_width;
+
+  if (DEEP && lo >= hi) {
+    // no keys fall to this split: say so, so that the merge skips it
+    if (tid < 16) {
+      float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
+      ml[0] = -INFINITY; ml[1] = 0.f;
+    }
+    return;
+  }
+
+  // queries -> shared memory (rows beyond M are zeros)
+  for (int idx = tid; idx < BM * CHUNKS; idx += THREADS) {
+    const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
+    const int m = m0 + row;
+    const bool ok = m < M;
+    const int tok = ok ? m / G : 0, hd = ok ? hk * G + (m - tok * G) : 0;
+    cp_async16(Qs + row * LDS + ch * 8, p.qkv + (size_t)(q0 + tok) * p.q_stride + (size_t)hd * D + ch * 8, ok);
+  }
+  const int kt0 = (lo / BN) * BN;
+  const int n_tiles = (hi - kt0 + BN - 1) / BN;
+  load_kv_tile(p, bt, hk, kt0, lo, hi, KVs, KVs + BN * LDS);
+  cp_async_commit();
+
+  // positions of this thread's two rows (g and g+8 of the warp's 16)
+  const int row_a = m0 + wm * 16 + g, row_b = row_a + 8;
+  const int pos_a = row_a < M ? p0 + row_a / G : -1, pos_b = row_b < M ? p0 + row_b / G : -1;
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int kt = kt0 + it * BN;
+    bf16* Ks = KVs + (it & 1) * 2 * BN * LDS;
+    bf16* Vs = Ks + BN * LDS;
+    if (it + 1 < n_tiles) {
+      bf16* Kn = KVs + ((it + 1) & 1) * 2 * BN * LDS;
+      load_kv_tile(p, bt, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    const int kbase = kt + wn * KW;                 // first key of this warp's share
+    const bool warp_has_keys = kbase < hi && kbase + KW > lo;
+    if (warp_has_keys) {
+      // S = Q K^T for 16 rows x KW keys
+      float s[NT][4];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4(a0, a1, a2, a3, Qs + (wm * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+          uint32_t b0, b1, b2, b3;   // (keys j*8.., d lo), (keys j*8.., d hi), (keys (j+1)*8.., d lo), (keys (j+1)*8.., d hi)
+          ldmatrix_x4(b0, b1, b2, b3, Ks + (wn * KW + j * 8 + (lane >> 4) * 8 + (lane & 7)) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[j], a0, a1, a2, a3, b0, b1);
+          mma_bf16(s[j + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      // scale, mask, running maximum
+      float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = kbase + j * 8 + tq * 2 + e;
+          const bool in_range = key >= lo && key < hi;
+          const bool ok_a = in_range && key <= pos_a && (p.window <= 0 || key > pos_a - p.window);
+          const bool ok_b = in_range && key <= pos_b && (p.window <= 0 || key > pos_b - p.window);
+          s[j][e] = ok_a ? s[j][e] * p.scale_log2 : -INFINITY;
+          s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+          mx_a = fmaxf(mx_a, s[j][e]);
+          mx_b = fmaxf(mx_b, s[j][2 + e]);
+        }
+      }
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+      const float al_a = (mn_a == -INFINITY) ? 1.f : exp2f(m_a - mn_a);
+      const float al_b = (mn_b == -INFINITY) ? 1.f : exp2f(m_b - mn_b);
+      m_a = mn_a; m_b = mn_b;
+      float sum_a = 0.f, sum_b = 0.f;
+      uint32_t pa[NT][2];   // probabilities as bfloat16 pairs: [j][0] rows g, [j][1] rows g+8
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const float p0_ = (s[j][0] == -INFINITY) ? 0.f : exp2f(s[j][0] - mn_a);
+        const float p1_ = (s[j][1] == -INFINITY) ? 0.f : exp2f(s[j][1] - mn_a);
+        const float p2_ = (s[j][2] == -INFINITY) ? 0.f : exp2f(s[j][2] - mn_b);
+        const float p3_ = (s[j][3] == -INFINITY) ? 0.f : exp2f(s[j][3] - mn_b);
+        sum_a += p0_ + p1_;
+        sum_b += p2_ + p3_;
+        pa[j][0] = pack_bf16(p0_, p1_);
+        pa[j][1] = pack_bf16(p2_, p3_);
+      }
+      l_a = l_a * al_a + sum_a;   // per-thread partial sums; the four threads of a row are added at the end
+      l_b = l_b * al_b + sum_b;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
+      }
+      // O += P V, 16 keys a step
+#pragma unroll
+      for (int ks = 0; ks < KW / 16; ++ks) {
+        const uint32_t a0 = pa[2 * ks][0], a1 = pa[2 * ks][1], a2 = pa[2 * ks + 1][0], a3 = pa[2 * ks + 1][1];
+#pragma unroll
+        for (int i = 0; i < D / 8; i += 2) {
+          uint32_t b0, b1, b2, b3;   // (keys lo, d i*8..), (keys hi, d i*8..), (keys lo, d (i+1)*8..), (keys hi, d (i+1)*8..)
+          ldmatrix_x4_trans(b0, b1, b2, b3, Vs + (wn * KW + ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + i * 8 + (lane >> 4) * 8);
+          mma_bf16(o[i], a0, a1, a2, a3, b0, b1);
+          mma_bf16(o[i + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+    __syncthreads();   // the stage may be overwritten by the next iteration's fetch
+  }
+
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+  if (!DEEP) {
+    const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+    if (row_a < M) {
+      const int tok = row_a / G, hd = hk * G + (row_a - tok * G);
+      bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)hd * D + tq * 2;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][0] * inv_a, o[i][1] * inv_a);
+    }
+    if (row_b < M) {
+      const int tok = row_b / G, hd = hk * G + (row_b - tok * G);
+      bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)hd * D + tq * 2;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2] * inv_b, o[i][3] * inv_b);
+    }
+    return;
+  } else {
+    // merge the four warps (each saw other keys) through shared memory, in float
+    float* Om = reinterpret_cast<float*>(smem_raw);           // [4][16][D]  (the stages are free now)
+    float* MLm = Om + 4 * 16 * D;                             // [4][16][2]
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      float* d0 = Om + ((size_t)warp * 16 + g) * D + i * 8 + tq * 2;
+      float* d1 = Om + ((size_t)warp * 16 + g + 8) * D + i * 8 + tq * 2;
+      d0[0] = o[i][0]; d0[1] = o[i][1];
+      d1[0] = o[i][2]; d1[1] = o[i][3];
+    }
+    if (tq == 0) {
+      MLm[(warp * 16 + g) * 2] = m_a;      MLm[(warp * 16 + g) * 2 + 1] = l_a;
+      MLm[(warp * 16 + g + 8) * 2] = m_b;  MLm[(warp * 16 + g + 8) * 2 + 1] = l_b;
+    }
+    __syncthreads();
+    const bool last = p.num_splits == 1;
+    for (int idx = tid; idx < 16 * D; idx += THREADS) {
+      const int row = idx / D, d = idx - row * D;
+      if (row >= M) continue;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, MLm[(w * 16 + row) * 2]);
+      float ll = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = MLm[(w * 16 + row) * 2];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+        ll += MLm[(w * 16 + row) * 2 + 1] * f;
+        acc += Om[((size_t)w * 16 + row) * D + d] * f;
+      }
+      if (last) {
+        const int tok = row / G, hd = hk * G + (row - tok * G);
+        p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      } else {
+        const size_t base = (((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + row;
+        p.part_o[base * D + d] = acc;
+        if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
+      }
+    }
+  }
+}
+
+// Merge the partial results of the key splits of the deep shape. grid (Hkv, R), 128 threads.
+__global__ void __launch_bounds__(THREADS) attention_merge_kernel(const Params p) {
+  const int r = blockIdx.y, hk = blockIdx.x;
+  const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
+  const int M = qn * p.G;
+  if (M > 16 || M <= 0) return;
+  const int S = p.num_splits;
+  const size_t base = ((size_t)r * p.Hkv + hk) * S;
+  for (int idx = threadIdx.x; idx < M * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float mm = -INFINITY;
+    for (int s = 0; s < S; ++s) mm = fmaxf(mm, p.part_ml[((base + s) * 16 + row) * 2]);
+    float ll = 0.f, acc = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float ms = p.part_ml[((base + s) * 16 + row) * 2];
+      if (ms == -INFINITY) continue;
+      const float f = exp2f(ms - mm);
+      ll += p.part_ml[((base + s) * 16 + row) * 2 + 1] * f;
+      acc += p.part_o[((base + s) * 16 + row) * D + d] * f;
+    }
+    const int tok = row / p.G, hd = hk * p.G + (row - tok * p.G);
+    p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+  }
+}
+
+template <int WM, int WN> size_t smem_bytes() {
+  const size_t tiles = (size_t)(WM * 16 + 4 * BN) * LDS * sizeof(bf16);
+  const size_t merge = WN > 1 ? (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float) : 0;
+  return tiles > merge ? tiles : merge;
+}
+
+}  // namespace
+
+SB_EXPORT int sb_attention_mma_head_dim() { return D; }
+
+// Bytes of scratch the deep shape needs for (n_rows, Hkv, num_splits): partial outputs, then (max, sum) pairs.
+SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_splits) {
+  if (num_splits <= 1) return 0;
+  return (long long)n_rows * Hkv * num_splits * 16 * (D + 2) * (long long)sizeof(float);
+}
+
+// which: bit 0 launch the wide shape, bit 1 launch the deep shape (with its merge if num_splits > 1).
+SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+                               const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
+                               void* out, int n_rows, int max_q, int which, int split_size, int num_splits, void* scratch,
+                               cudaStream_t stream) {
+  if (n_rows <= 0 || max_q <= 0) return 0;
+  if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
+  if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
+  if ((q_stride % 8) || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || !aligned16(out)) return SB_ERR_ALIGN;
+  Params p;
+  p.qkv = (const bf16*)qkv; p.q_stride = q_stride; p.kc = (const bf16*)kc; p.vc = (const bf16*)vc;
+  p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
+  p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
+  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
+  p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr;
+  if (which & 1) {
+    auto k = attention_mma_kernel<4, 1>;
+    const size_t smem = smem_bytes<4, 1>();
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const long long tiles = ((long long)max_q * p.G + 63) / 64;
+    if (tiles > 2147483647LL) return SB_ERR_LIMIT;
+    k<<<dim3((unsigned)tiles, Hkv, n_rows), THREADS, smem, stream>>>(p);
+    SB_LAUNCH_CHECK();
+  }
+  if (which & 2) {
+    if (p.G > 16) return SB_ERR_SHAPE;   // the caller sends such groups to the wide shape
+    if (num_splits < 1 || split_size <= 0 || (split_size % BN)) return SB_ERR_SHAPE;
+    if (num_splits > 1) {
+      if (!scratch) return SB_ERR_SHAPE;
+      p.part_o = (float*)scratch;
+      p.part_ml = p.part_o + (size_t)n_rows * Hkv * num_splits * 16 * D;
+    }
+    auto k = attention_mma_kernel<1, 4>;
+    const size_t smem = smem_bytes<1, 4>();
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<dim3(num_splits, Hkv, n_rows), THREADS, smem, stream>>>(p);
+    SB_LAUNCH_CHECK();
+    if (num_splits > 1) {
+      attention_merge_kernel<<<dim3(Hkv, n_rows), THREADS, 0, stream>>>(p);
+      SB_LAUNCH_CHECK();
+    }
+  }
+  return 0;
+}

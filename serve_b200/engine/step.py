@@ -32,6 +32,7 @@ class BatchShape:
     rows: int          # requests in the step
     tokens: int        # tokens in the step
     max_q: int         # most tokens any request brings
+    min_q: int         # fewest tokens any request brings
     max_kv: int        # longest sequence after the step
     pure_decode: bool  # every request brings exactly one token
 
@@ -197,7 +198,7 @@ class Stepper:
 
         ctx = StepContext(
             rt=self.rt,
-            shape=BatchShape(r, t, max(q_lens), max(new_lens), pure_decode),
+            shape=BatchShape(r, t, max(q_lens), min(q_lens), max(new_lens), pure_decode),
             tokens=view("tokens"), positions=view("positions"), token_row=view("token_row"),
             cu_q=view("cu_q"), kv_len=view("kv_len"), slots=view("slots"), logit_rows=view("logit_rows"),
             block_tables=[dev[off: off + rr * w].view(rr, w) for off, rr, w in lay.tables],
@@ -221,7 +222,7 @@ class Stepper:
         """
         g = self._graphs.get(r)
         if g is None:
-            shape = BatchShape(r, r, 1, self.cache.max_context, True)
+            shape = BatchShape(r, r, 1, 1, self.cache.max_context, True)
             static_ctx = StepContext(**{**ctx.__dict__, "shape": shape})
             # warm up outside capture (allocator pools, cuBLAS workspaces, lazy module loads)
             s = torch.cuda.Stream(device=self.rt.device)

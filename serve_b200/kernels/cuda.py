@@ -52,7 +52,8 @@ def core_jobs():
 
 
 def attention_job(head_dim: int):
-    return {"name": f"sb_attention_hd{head_dim}", "sources": ["attention_simt.cu"], "defines": [f"SB_HEAD_DIM={head_dim}"]}
+    return {"name": f"sb_attention_hd{head_dim}", "sources": ["attention_simt.cu", "attention_mma.cu"],
+            "defines": [f"SB_HEAD_DIM={head_dim}"]}
 
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -78,8 +79,10 @@ class CudaKernels:
         self._attn: Dict[int, ctypes.CDLL] = {}
         for d in set(head_dims):
             self._attn[d] = ctypes.CDLL(paths[f"sb_attention_hd{d}"])
+            self._attn[d].sb_attention_mma_scratch_bytes.restype = ctypes.c_longlong
         self._verbose = verbose
         self._errors: Optional[torch.Tensor] = None
+        self.force_simt_attention = False   # tests: run bfloat16 through the plain-arithmetic kernel
         self.launches = 0         # launches of this engine's own kernels
         self.library_calls = 0    # library matrix products
 
@@ -102,6 +105,7 @@ class CudaKernels:
             path = build.build_library(**job)
             self.paths[job["name"]] = path
             lib = self._attn[head_dim] = ctypes.CDLL(path)
+            lib.sb_attention_mma_scratch_bytes.restype = ctypes.c_longlong
         return lib
 
     def errors_tensor(self) -> torch.Tensor:
@@ -157,11 +161,44 @@ class CudaKernels:
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
                   page_size, scale, window, out, shape) -> None:
         lib = self._attention_lib(head_dim)
+        if qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
+            return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
+                                       page_size, scale, window, out, shape)
         self.launches += 1
         _check(lib.sb_attention_simt(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
             _DT[qkv.dtype], _stream()), "attention")
+
+    # Blocks the deep shape aims at: a few per SM, so that key splits fill the 148 SMs at small batches.
+    TARGET_BLOCKS = 148 * 4
+
+    def split_plan(self, rows: int, kv_heads: int, max_kv: int):
+        """(split_size, num_splits) of the deep shape for a batch; a function of sizes only, never of data."""
+        want = max(1, self.TARGET_BLOCKS // max(1, rows * kv_heads))
+        split_size = max(128, -(-(-(-max_kv // want)) // 64) * 64)
+        return split_size, max(1, -(-max_kv // split_size))
+
+    def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
+                       scale, window, out, shape) -> None:
+        group = heads // kv_heads
+        min_q = getattr(shape, "min_q", 1)
+        which = 0
+        if group > 16 or shape.max_q * group > 16:
+            which |= 1
+        if group <= 16 and min_q * group <= 16:
+            which |= 2
+        split_size, num_splits, scratch = 64, 1, None
+        if which & 2:
+            split_size, num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
+            if num_splits > 1:
+                nbytes = lib.sb_attention_mma_scratch_bytes(shape.rows, kv_heads, num_splits)
+                scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
+        self.launches += (which & 1) + ((which >> 1) & 1) * (2 if num_splits > 1 else 1)
+        _check(lib.sb_attention_mma(
+            _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
+            heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
+            which, split_size, num_splits, _p(scratch), _stream()), "attention")
 
     def sample(self, logits, temperature, req_ids, tok_index, seed, out) -> None:
         self.launches += 1

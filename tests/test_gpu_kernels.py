@@ -26,8 +26,8 @@ E = EmuKernels(DEV)
 
 
 class Shape:
-    def __init__(self, rows, tokens, max_q, max_kv, pure_decode=False):
-        self.rows, self.tokens, self.max_q, self.max_kv, self.pure_decode = rows, tokens, max_q, max_kv, pure_decode
+    def __init__(self, rows, tokens, max_q, max_kv, pure_decode=False, min_q=1):
+        self.rows, self.tokens, self.max_q, self.max_kv, self.pure_decode, self.min_q = rows, tokens, max_q, max_kv, pure_decode, min_q
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -123,7 +123,7 @@ def _paged_setup(dtype, heads, kv_heads, d, page, q_lens, kv_lens, num_pages=Non
     row = torch.cat([torch.full((q,), i) for i, q in enumerate(q_lens)]).to(torch.int32)
     to = lambda x: x.to(DEV)
     return dict(qkv=to(qkv), kc=to(kc), vc=to(vc), bt=to(bt), cu=to(cu), kv=to(torch.tensor(kv_lens, dtype=torch.int32)),
-                pos=to(pos), row=to(row), shape=Shape(r, t, max(q_lens), max(kv_lens), all(q == 1 for q in q_lens)))
+                pos=to(pos), row=to(row), shape=Shape(r, t, max(q_lens), max(kv_lens), all(q == 1 for q in q_lens), min(q_lens)))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -131,7 +131,6 @@ def _paged_setup(dtype, heads, kv_heads, d, page, q_lens, kv_lens, num_pages=Non
     (5, 1, 48, 48, 0, 16), (6, 3, 32, 32, 1, 8), (4, 4, 80, 40, 0, 5), (8, 2, 64, 64, 0, 64), (3, 3, 16, 0, 0, 4)])
 def test_rope_cache_write(K, dtype, heads, kv_heads, d, rot, pairing, page):
     s = _paged_setup(dtype, heads, kv_heads, d, page, q_lens=[7, 1, 20], kv_lens=[7, 33, 52])
-    s["pos"][0] = 100_000 % 1 + s["pos"][0]       # positions as they are
     inv = (1.0 / (10000.0 ** (torch.arange(0, max(rot, 2), 2).float() / max(rot, 2)))).to(DEV)
     a = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in s.items()}
     b = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in s.items()}
@@ -275,3 +274,68 @@ def test_sampling_distribution(K):
     freq = torch.bincount(out.long(), minlength=5).float() / 4000
     want = torch.softmax(logits[0] / 0.7, -1)
     assert float((freq - want).abs().max()) < 0.03
+
+
+MMA_CASES = [
+    # heads, kv, d, page, q_lens, kv_lens, window : shapes that reach both block shapes, the split of keys and its merge
+    (32, 8, 64, 64, [1] * 8, [2176, 100, 64, 65, 1, 4000, 513, 128], 0),       # decoding, long contexts, many splits
+    (32, 8, 64, 64, [1], [3000], 0),                                          # batch 1
+    (32, 8, 64, 16, [300, 1, 2, 4, 5, 64], [300, 700, 50, 4, 900, 1000], 0),  # portions beside decoded tokens
+    (24, 8, 128, 32, [130, 1, 3], [130, 260, 131], 0),
+    (5, 1, 48, 16, [40, 1, 3, 4], [41, 99, 200, 4], 0),                       # group of 5: 3 tokens fit the deep shape, 4 do not
+    (40, 2, 32, 8, [1, 9], [77, 30], 0),                                      # group of 20: wide shape only
+    (6, 6, 80, 8, [1, 16, 17], [500, 16, 300], 0),                            # no grouping
+    (4, 2, 256, 16, [70, 1], [70, 333], 0),
+    (8, 4, 16, 4, [3, 129], [1000, 129], 0),
+    (8, 2, 64, 8, [60, 1, 2], [200, 400, 90], 37),                            # windows
+    (8, 2, 64, 64, [1, 1], [1000, 40], 128),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES, ids=[f"h{c[0]}kv{c[1]}d{c[2]}p{c[3]}w{c[6]}n{len(c[4])}" for c in MMA_CASES])
+def test_attention_tensor_cores_against_plain_arithmetic(K, case):
+    """bfloat16: the tensor-core kernel against the plain-arithmetic kernel and the torch version."""
+    heads, kv_heads, d, page, q_lens, kv_lens, window = case
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens, kv_lens)
+    s["kc"][torch.rand(s["kc"].shape[:2], device=DEV) < 0.0] = 0     # (keeps shapes; values stay random)
+    t = sum(q_lens)
+    scale = 1.0 / math.sqrt(d)
+    outs = {}
+    for name in ("mma", "simt", "torch"):
+        out = torch.full((t, heads * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        if name == "torch":
+            E.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, window, out, s["shape"])
+        else:
+            K.force_simt_attention = name == "simt"
+            try:
+                K.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, window, out, s["shape"])
+            finally:
+                K.force_simt_attention = False
+        outs[name] = out.float()
+    assert bool(torch.isfinite(outs["mma"]).all()), "a row was not written, or NaN"
+    torch.testing.assert_close(outs["simt"], outs["torch"], atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(outs["mma"], outs["torch"], atol=2e-2, rtol=2e-2)
+
+
+def test_attention_unwritten_cache_does_not_leak(K):
+    """Pages hold NaN wherever nothing was written (beyond each request's length): outputs stay finite."""
+    heads, kv_heads, d, page = 8, 2, 64, 16
+    q_lens, kv_lens = [1, 5, 40], [70, 21, 40]
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens, kv_lens)
+    for r, L in enumerate(kv_lens):
+        for b in range(-(-L // page)):
+            pg = int(s["bt"][r, b])
+            lo = max(0, L - b * page)
+            if lo < page:
+                s["kc"][pg, lo:] = float("nan")
+                s["vc"][pg, lo:] = float("nan")
+    used = set(int(x) for x in s["bt"].flatten().tolist() if x >= 0)
+    for pg in range(s["kc"].shape[0]):
+        if pg not in used:
+            s["kc"][pg] = float("nan"); s["vc"][pg] = float("nan")
+    out = torch.zeros(sum(q_lens), heads * d, device=DEV, dtype=torch.bfloat16)
+    ref = torch.zeros_like(out)
+    K.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, 0.125, 0, out, s["shape"])
+    E.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, 0.125, 0, ref, s["shape"])
+    assert bool(torch.isfinite(out.float()).all())
+    torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
