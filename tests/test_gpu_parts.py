@@ -1,0 +1,250 @@
+"""Each part of a layer alone on the GPU against the plain implementation's function for it, and parts
+defined here (outside the framework) registered, built and stepped: a mixer with state of its own,
+a feed-forward with routing, another position encoding."""
+import math
+
+import pytest
+import torch
+
+from serve_b200.cache import CacheManager
+from serve_b200.config import EngineConfig, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from serve_b200.engine import Engine, StepEntry
+from serve_b200.engine.runtime import Runtime
+from serve_b200.engine.step import BatchShape, StepContext
+from serve_b200.parts import CacheNeed, FeedForward, Mixer, PositionEncoding, TensorDecl, build_part, register_part
+from tests import helpers
+from tests.plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _rt(dtype):
+    from serve_b200.kernels import load_kernels
+
+    return Runtime(load_kernels(DEV), DEV, DT[dtype])
+
+
+def _ctx(rt, q_lens, starts, mgr=None, rids=None):
+    t = sum(q_lens)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    pos = [s + j for q, s in zip(q_lens, starts) for j in range(q)]
+    row = [i for i, q in enumerate(q_lens) for _ in range(q)]
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + q)
+    kv = [s + q for q, s in zip(q_lens, starts)]
+    tables = []
+    if mgr is not None:
+        tables = [torch.from_numpy(mgr.table_rows(g, rids)).to(DEV) for g in range(len(mgr.groups))]
+    return StepContext(rt=rt, shape=BatchShape(len(q_lens), t, max(q_lens), min(q_lens), max(kv), all(q == 1 for q in q_lens)),
+                       tokens=i32([0] * t), positions=i32(pos), token_row=i32(row), cu_q=i32(cu), kv_len=i32(kv),
+                       slots=i32(list(range(len(q_lens)))), logit_rows=i32([]), block_tables=tables, rids=rids or [])
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-6), ("bfloat16", 3e-2)])
+def test_norm_part(dtype, tol):
+    rt = _rt(dtype)
+    norm = build_part("norm", PartSpec("rms", {"size": 200, "eps": 3e-4}, prefix="n."), rt)
+    assert [d.name for d in norm.tensor_decls()] == ["n.weight"] and norm.tensor_decls()[0].role == "vector"
+    w = (1 + 0.2 * torch.randn(200)).to(DEV)
+    norm.load({"n.weight": w})
+    x = torch.randn(9, 200, device=DEV) * 2
+    delta = torch.randn(9, 200, device=DEV).to(DT[dtype])
+    want = P.rms_norm(x + delta.float(), w, 3e-4)
+    x_in = x.clone()
+    got = norm.forward(x_in, delta, None)
+    torch.testing.assert_close(x_in, x + delta.float())
+    torch.testing.assert_close(got.float(), want, atol=tol, rtol=tol)
+
+
+def _bf16_tol(want):
+    """bfloat16 keeps 8 bits: the bound is 2^-6 of the largest value, the rule the replay tests use for logits."""
+    return float(want.abs().max()) * 2.0 ** -6
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", None)])
+def test_feed_forward_part(dtype, tol):
+    rt = _rt(dtype)
+    ff = build_part("feed_forward", PartSpec("swiglu", {"hidden": 120, "intermediate": 200}, prefix="m."), rt)
+    w = {d.name: (torch.randn(d.shape) * 0.2).to(DEV).to(DT[dtype]) for d in ff.tensor_decls()}
+    ff.load(w)
+    h = torch.randn(13, 120, device=DEV).to(DT[dtype])
+    want = P.swiglu(h.float(), w["m.gate_proj.weight"].float(), w["m.up_proj.weight"].float(), w["m.down_proj.weight"].float())
+    tol = tol or _bf16_tol(want)
+    torch.testing.assert_close(ff.forward(h, None).float(), want, atol=tol, rtol=0)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", None)])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_in_two_portions(dtype, tol, window):
+    """The mixer alone: 21 tokens in one go, then 9 more; against whole-sequence attention of the plain code."""
+    rt = _rt(dtype)
+    heads, kv_heads, d, hidden = 6, 2, 48, 120
+    scaling = dict(factor=4.0, low_freq_factor=1.0, high_freq_factor=8.0, original_max_position_embeddings=32)
+    spec = PartSpec("attention", {"hidden": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": d, "scale": None, "window": window,
+                                  "position": PartSpec("rotary", {"rotary_dim": d, "theta": 25000.0, "scaling": scaling, "pairing": "half"})},
+                    prefix="a.")
+    att = build_part("mixer", spec, rt)
+    w = {dcl.name: (torch.randn(dcl.shape) * 0.15).to(DEV).to(DT[dtype]) for dcl in att.tensor_decls()}
+    att.load(w)
+    need = att.cache_need()
+    assert need == CacheNeed(kv_heads, d, window)
+    mgr = CacheManager([need], [None], 8, 16, 2, 128, device=DEV, kv_dtype=DT[dtype])
+    view = mgr.views()[0]
+    x = torch.randn(30, hidden, device=DEV).to(DT[dtype])
+    cfg = dict(num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=d)
+    inv = P.rope_inv_freq(d, 25000.0, dict(rope_type="llama3", **scaling))
+    want, _ = P.attention_layer(x.float().cpu(), {k: v.float().cpu() for k, v in w.items()}, "a.", cfg, torch.arange(30), inv, window)
+    mgr.open("r")
+    outs = []
+    for start, n in ((0, 21), (21, 9)):
+        mgr.reserve([("r", start + n)])
+        outs.append(att.forward(x[start:start + n], _ctx(rt, [n], [start], mgr, ["r"]), view))
+        mgr.commit("r", start + n)
+    rt.kernels.check_errors()
+    tol = tol or _bf16_tol(want)
+    torch.testing.assert_close(torch.cat(outs).float().cpu(), want, atol=tol, rtol=0)
+    if window:
+        assert mgr.groups[0].pool.in_use < mgr.blocks_for(30), "pages the window has passed go back to the pool"
+
+
+def test_position_part_matches_plain_frequencies():
+    rt = _rt("float32")
+    sc = dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=64)
+    rot = build_part("position", PartSpec("rotary", {"rotary_dim": 32, "theta": 500000.0, "scaling": sc}), rt)
+    torch.testing.assert_close(rot.inv_freq.cpu(), P.rope_inv_freq(32, 500000.0, dict(rope_type="llama3", **sc)), atol=0, rtol=2e-7)
+
+
+# ---- parts of other kinds, defined here, never part of any model of the framework ----------------------
+@register_part("mixer", "test_running_mean")
+class RunningMeanMixer(Mixer):
+    """A toy mixer with per-request state of fixed size: out_t = W * mean(h_0..h_t). State: sum [hidden] and count [1]."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec.params["hidden"])
+        self.w = None
+
+    def tensor_decls(self):
+        return [TensorDecl(self.prefix + "mix.weight", (self.hidden, self.hidden))]
+
+    def load(self, tensors):
+        self.w = tensors[self.prefix + "mix.weight"]
+
+    def cache_need(self):
+        return CacheNeed(state_shape=(self.hidden + 1,))
+
+    def forward(self, h, ctx, cache):
+        out = torch.empty_like(h)
+        cu = ctx.cu_q.tolist()
+        for r, slot in enumerate(ctx.slots.tolist()):
+            a, b = cu[r], cu[r + 1]
+            st = cache.state[slot]
+            sums = st[: self.hidden] + torch.cumsum(h[a:b].float(), 0)
+            counts = st[self.hidden] + torch.arange(1, b - a + 1, device=h.device)
+            out[a:b] = ((sums / counts[:, None]) @ self.w.float().T).to(h.dtype)
+            st[: self.hidden] = sums[-1]
+            st[self.hidden] = counts[-1]
+        return out
+
+
+@register_part("feed_forward", "test_top1_experts")
+class Top1Experts(FeedForward):
+    """A toy routed feed-forward: router logits in float32, the best expert's matrix is applied."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden, self.experts = int(spec.params["hidden"]), int(spec.params["experts"])
+
+    def tensor_decls(self):
+        return [TensorDecl(self.prefix + "router.weight", (self.experts, self.hidden)),
+                TensorDecl(self.prefix + "experts.weight", (self.experts * self.hidden, self.hidden))]
+
+    def load(self, tensors):
+        self.router = tensors[self.prefix + "router.weight"]
+        self.w = tensors[self.prefix + "experts.weight"].view(self.experts, self.hidden, self.hidden)
+
+    def forward(self, h, ctx):
+        pick = (h.float() @ self.router.float().T).argmax(-1)
+        return torch.einsum("th,tch->tc", h.float(), self.w.float()[pick]).to(h.dtype)
+
+
+@register_part("position", "test_none_but_marker")
+class MarkerPosition(PositionEncoding):
+    """Another position encoding for the attention mixer: no rotation at all (rotary_dim 0)."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.rotary_dim, self.pairing = 0, 0
+        self.inv_freq = torch.zeros(1, dtype=torch.float32, device=runtime.device)
+
+
+def _toy_spec(hidden, vocab):
+    norm = lambda p: PartSpec("rms", {"size": hidden, "eps": 1e-5}, prefix=p)
+    att = PartSpec("attention", {"hidden": hidden, "heads": 4, "kv_heads": 2, "head_dim": 16, "scale": None, "window": None,
+                                 "position": PartSpec("test_none_but_marker", {})}, prefix="l1.att.")
+    layers = [
+        LayerSpec("pre_norm", PartSpec("test_running_mean", {"hidden": hidden}, prefix="l0."),
+                  PartSpec("test_top1_experts", {"hidden": hidden, "experts": 3}, prefix="l0.moe."), norm("l0.n1."), norm("l0.n2.")),
+        LayerSpec("pre_norm", att, PartSpec("swiglu", {"hidden": hidden, "intermediate": 96}, prefix="l1.mlp."), norm("l1.n1."), norm("l1.n2.")),
+    ]
+    return ModelSpec("ToyForTests", hidden, vocab, PartSpec("table", {"vocab": vocab, "hidden": hidden, "name": "emb.weight"}),
+                     layers, [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)], norm("final."),
+                     PartSpec("linear", {"vocab": vocab, "hidden": hidden, "name": "head.weight", "tied_to": "emb.weight"}), 512)
+
+
+def _toy_plain(w, tokens, hidden):
+    """The same toy model, whole sequence, plain torch on the CPU."""
+    x = w["emb.weight"][tokens]
+    t = x.shape[0]
+    def mean_mix(h):
+        return (torch.cumsum(h, 0) / torch.arange(1, t + 1)[:, None]) @ w["l0.mix.weight"].T
+    def moe(h):
+        pick = (h @ w["l0.moe.router.weight"].T).argmax(-1)
+        return torch.einsum("th,tch->tc", h, w["l0.moe.experts.weight"].view(3, hidden, hidden)[pick])
+    def layer0(x):
+        x = x + mean_mix(P.rms_norm(x, w["l0.n1.weight"], 1e-5))
+        return x + moe(P.rms_norm(x, w["l0.n2.weight"], 1e-5))
+    x = layer0(x)
+    h = P.rms_norm(x, w["l1.n1.weight"], 1e-5)
+    q = (h @ w["l1.att.q_proj.weight"].T).view(t, 4, 16)
+    k = (h @ w["l1.att.k_proj.weight"].T).view(t, 2, 16)
+    v = (h @ w["l1.att.v_proj.weight"].T).view(t, 2, 16)
+    x = x + P.causal_attention(q, k, v, 0.25).reshape(t, 64) @ w["l1.att.o_proj.weight"].T
+    x = x + P.swiglu(P.rms_norm(x, w["l1.n2.weight"], 1e-5), w["l1.mlp.gate_proj.weight"], w["l1.mlp.up_proj.weight"], w["l1.mlp.down_proj.weight"])
+    x = layer0(x)
+    return P.rms_norm(x, w["final.weight"], 1e-5) @ w["emb.weight"].T
+
+
+def test_toy_parts_are_registered_built_and_stepped():
+    """A model made of parts defined in this file runs through the engine's step function, cut in portions and
+    mixed with another request, and equals its plain whole-sequence version. No framework file knows these parts."""
+    from serve_b200.config.llama import LlamaConfig
+    from serve_b200.weights.loader import load_from_source
+    from serve_b200.weights.random_init import random_tensor
+
+    hidden, vocab = 64, 97
+    spec = _toy_spec(hidden, vocab)
+    ec = EngineConfig(dtype="float32", page_size=8, num_pages=24, max_slots=3, max_tokens_per_step=128, max_context=128, use_cuda_graphs=False)
+    eng = Engine(config=None, engine_config=ec, spec=spec)
+    made = {}
+    def source(decl):
+        made[decl.name] = random_tensor(decl, seed=5, std=0.3, norm_std=0.1)
+        return made[decl.name]
+    load_from_source(eng.model, source, torch.float32, DEV)
+    eng._make_cache()
+    needs = eng.model.cache_needs()
+    assert needs[0].state_shape == (hidden + 1,) and needs[1].has_pages and needs[2].state_shape == (hidden + 1,)
+    assert eng.stepper.views[0].state is not eng.stepper.views[2].state     # the layer run twice has a state per run
+    reqs = {"x": helpers.random_tokens(vocab, 41, 1), "y": helpers.random_tokens(vocab, 23, 2), "z": helpers.random_tokens(vocab, 30, 3)}
+    plain = {rid: _toy_plain(made, torch.tensor(t), hidden) for rid, t in reqs.items()}
+    with torch.inference_mode():
+        got = helpers.replay(eng, helpers.trace_mixed(reqs, live=2, seed=3, budget=24))
+    helpers.compare_with_plain(got, plain, atol=2e-4)
+    assert eng.cache.live == 0
+    # a slot handed out again starts from zeroed state: replay once more on the used engine
+    with torch.inference_mode():
+        got = helpers.replay(eng, helpers.trace_portions(reqs, sizes=(5, 2, 11)))
+    helpers.compare_with_plain(got, plain, atol=2e-4)
