@@ -50,7 +50,7 @@ def build_dir() -> str:
     for d in candidates:
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
+            probe = os.path.join(d, f".w{os.getpid()}.{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.remove(probe)
