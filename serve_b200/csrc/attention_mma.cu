@@ -72,7 +72,48 @@ struct Params {
   int split_size, num_splits;
   float* part_o;    // [R, Hkv, splits, 16, D]
   float* part_ml;   // [R, Hkv, splits, 16, 2]
+  int* tickets;     // [R, Hkv] zero before the launch and again after it; nullptr: a separate kernel merges
 };
+
+// Partial results of all key splits of (request r, kv head hk) -> the output rows. Reads bypass L1: the
+// partials were written by other SMs.
+__device__ __forceinline__ void merge_splits(const Params& p, int r, int hk, int q0, int M) {
+  const int S = p.num_splits;
+  const size_t base = ((size_t)r * p.Hkv + hk) * S;
+  for (int idx = threadIdx.x; idx < M * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float mm = -INFINITY;
+    for (int s = 0; s < S; ++s) mm = fmaxf(mm, __ldcg(p.part_ml + ((base + s) * 16 + row) * 2));
+    float ll = 0.f, acc = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float ms = __ldcg(p.part_ml + ((base + s) * 16 + row) * 2);
+      if (ms == -INFINITY) continue;
+      const float f = exp2f(ms - mm);
+      ll += __ldcg(p.part_ml + ((base + s) * 16 + row) * 2 + 1) * f;
+      acc += __ldcg(p.part_o + ((base + s) * 16 + row) * D + d) * f;
+    }
+    const int tok = row / p.G, hd = hk * p.G + (row - tok * p.G);
+    p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+  }
+}
+
+// Called by every block of a split launch once its partial results are written: the block that arrives last
+// merges. Nobody waits for anybody.
+__device__ __forceinline__ void finish_split(const Params& p, int r, int hk, int q0, int M) {
+  if (p.tickets == nullptr) return;
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(p.tickets + (size_t)r * p.Hkv + hk, 1);
+    s_last = (t == p.num_splits - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  merge_splits(p, r, hk, q0, M);
+  if (threadIdx.x == 0) p.tickets[(size_t)r * p.Hkv + hk] = 0;
+}
 
 // Fetch keys [kt, kt+BN) of kv head hk into one stage of shared memory; keys outside [lo, hi) become zeros.
 __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int hk, int kt, int lo, int hi, bf16* Ks, bf16* Vs) {
@@ -139,6 +180,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
       float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
       ml[0] = -INFINITY; ml[1] = 0.f;
     }
+    if (p.num_splits > 1) finish_split(p, r, hk, q0, M);
     return;
   }
 
@@ -316,6 +358,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
         if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
       }
     }
+    if (!last) finish_split(p, r, hk, q0, M);
   }
 }
 
@@ -325,23 +368,7 @@ __global__ void __launch_bounds__(THREADS) attention_merge_kernel(const Params p
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int M = qn * p.G;
   if (M > 16 || M <= 0) return;
-  const int S = p.num_splits;
-  const size_t base = ((size_t)r * p.Hkv + hk) * S;
-  for (int idx = threadIdx.x; idx < M * D; idx += THREADS) {
-    const int row = idx / D, d = idx - row * D;
-    float mm = -INFINITY;
-    for (int s = 0; s < S; ++s) mm = fmaxf(mm, p.part_ml[((base + s) * 16 + row) * 2]);
-    float ll = 0.f, acc = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float ms = p.part_ml[((base + s) * 16 + row) * 2];
-      if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - mm);
-      ll += p.part_ml[((base + s) * 16 + row) * 2 + 1] * f;
-      acc += p.part_o[((base + s) * 16 + row) * D + d] * f;
-    }
-    const int tok = row / p.G, hd = hk * p.G + (row - tok * p.G);
-    p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
-  }
+  merge_splits(p, r, hk, q0, M);
 }
 
 template <int WM, int WN> size_t smem_bytes() {
@@ -360,11 +387,13 @@ SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_
   return (long long)n_rows * Hkv * num_splits * 16 * (D + 2) * (long long)sizeof(float);
 }
 
-// which: bit 0 launch the wide shape, bit 1 launch the deep shape (with its merge if num_splits > 1).
+// which: bit 0 launch the wide shape, bit 1 launch the deep shape. With num_splits > 1 the deep shape needs
+// ``scratch`` (sb_attention_mma_scratch_bytes) and merges either in the block that finishes last (tickets: n_rows * Hkv
+// ints, zero before the first launch; every launch leaves them zero) or, with tickets == nullptr, in a second kernel.
 SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
                                const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
                                void* out, int n_rows, int max_q, int which, int split_size, int num_splits, void* scratch,
-                               cudaStream_t stream) {
+                               int* tickets, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -374,7 +403,7 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
-  p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr;
+  p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   if (which & 1) {
     auto k = attention_mma_kernel<4, 1>;
     const size_t smem = smem_bytes<4, 1>();
@@ -391,13 +420,14 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
       if (!scratch) return SB_ERR_SHAPE;
       p.part_o = (float*)scratch;
       p.part_ml = p.part_o + (size_t)n_rows * Hkv * num_splits * 16 * D;
+      p.tickets = tickets;
     }
     auto k = attention_mma_kernel<1, 4>;
     const size_t smem = smem_bytes<1, 4>();
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     k<<<dim3(num_splits, Hkv, n_rows), THREADS, smem, stream>>>(p);
     SB_LAUNCH_CHECK();
-    if (num_splits > 1) {
+    if (num_splits > 1 && tickets == nullptr) {
       attention_merge_kernel<<<dim3(Hkv, n_rows), THREADS, 0, stream>>>(p);
       SB_LAUNCH_CHECK();
     }

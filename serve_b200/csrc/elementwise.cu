@@ -66,9 +66,95 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   }
 }
 
+// The same for widths that are a multiple of 4 and fit 8 float4 per thread: the row stays in registers, the
+// weight is fetched before the reduction, loads are 16 bytes (8 for bfloat16).
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+template <typename T, typename W, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
+                                       const W* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const int src_row = rows ? rows[b] : b;
+  float* xr = x + (size_t)src_row * dim;
+  const T* dr = delta ? delta + (size_t)src_row * dim : nullptr;
+  const int nvec = dim >> 2;
+  float4 v[VPT], wv[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) {
+      v[k] = Vec4<float>::load(xr + i * 4);
+      wv[k] = Vec4<W>::load(weight + i * 4);
+      if (dr) {
+        const float4 d = Vec4<T>::load(dr + i * 4);
+        v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+      }
+    }
+  }
+  // the sum of squares is taken in index order within a thread and in a fixed tree across threads
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  T* orow = out + (size_t)b * dim;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) {
+      if (!rows && dr) Vec4<float>::store(xr + i * 4, v[k]);
+      Vec4<T>::store(orow + i * 4, make_float4(v[k].x * inv * wv[k].x, v[k].y * inv * wv[k].y, v[k].z * inv * wv[k].z,
+                                               v[k].w * inv * wv[k].w));
+    }
+  }
+}
+
 template <typename T>
 static int launch_add_rmsnorm(float* x, const void* delta, const int* rows, const void* weight, int weight_dtype, void* out,
                               int n_rows, int dim, float eps, cudaStream_t stream) {
+  if ((dim % 4) == 0 && aligned16(x) && aligned16(out) && aligned16(weight) && (!delta || aligned16(delta))) {
+    // vector path: threads so that each holds at most 2 (or 8) float4
+    const int nvec = dim / 4;
+    int threads = nvec <= 128 ? 128 : (nvec <= 256 ? 256 : 512);
+    const int vpt = (nvec + threads - 1) / threads;
+    if (vpt <= 8) {
+#define SB_NORM_VEC(WT, VPT)                                                                                              \
+  add_rmsnorm_vec_kernel<T, WT, VPT><<<n_rows, threads, 0, stream>>>(x, (const T*)delta, rows, (const WT*)weight, (T*)out, \
+                                                                     dim, eps)
+      if (weight_dtype == SB_DTYPE_F32) {
+        if (vpt <= 1) SB_NORM_VEC(float, 1); else if (vpt <= 2) SB_NORM_VEC(float, 2); else SB_NORM_VEC(float, 8);
+      } else if (weight_dtype == SB_DTYPE_BF16) {
+        if (vpt <= 1) SB_NORM_VEC(__nv_bfloat16, 1); else if (vpt <= 2) SB_NORM_VEC(__nv_bfloat16, 2); else SB_NORM_VEC(__nv_bfloat16, 8);
+      } else {
+        return SB_ERR_DTYPE;
+      }
+#undef SB_NORM_VEC
+      SB_LAUNCH_CHECK();
+      return 0;
+    }
+  }
   const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   const size_t smem = (size_t)dim * sizeof(float);
   if (smem > 200 * 1024) return SB_ERR_LIMIT;
@@ -134,11 +220,15 @@ SB_EXPORT int sb_swiglu(const void* gate_up, void* out, int n_tokens, int inter,
 // block_table[row, pos / ps]. pairing 0: pairs (j, j + rot/2); 1: (2j, 2j+1).
 // A page id < 0 or a block index beyond the table is counted in *errors and
 // the write is skipped.
+constexpr int ROPE_THREADS = 128;
+
+// grid (tokens, y): blocks y < rot_blocks each rotate ROPE_THREADS (head, pair) items of q and k; the
+// remaining blocks copy v (and the part of k beyond the rotary width) into the page.
 template <typename T>
-__global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ token_row,
-                                        const float* __restrict__ inv_freq, int pairing, int rot, int H, int Hkv, int D,
-                                        T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ block_table, int bt_width,
-                                        int ps, int num_pages, int write_cache, int* __restrict__ errors) {
+__global__ void __launch_bounds__(ROPE_THREADS) rope_cache_write_kernel(
+    T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ token_row, const float* __restrict__ inv_freq,
+    int pairing, int rot, int H, int Hkv, int D, T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ block_table,
+    int bt_width, int ps, int num_pages, int write_cache, int rot_blocks, int* __restrict__ errors) {
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rot >> 1;
@@ -148,22 +238,22 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
   if (write_cache) {
     const int blk = pos / ps;
     const int r = token_row[t];
-    int page = (blk < bt_width && pos >= 0) ? block_table[(size_t)r * bt_width + blk] : -1;
+    const int page = (blk < bt_width && pos >= 0) ? block_table[(size_t)r * bt_width + blk] : -1;
     cache_ok = page >= 0 && page < num_pages;
-    if (!cache_ok && threadIdx.x == 0) atomicAdd(errors, 1);
+    if (!cache_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicAdd(errors, 1);
     cache_base = ((size_t)(cache_ok ? page : 0) * ps + (pos % ps)) * Hkv * D;
   }
-  // rotated pairs of q heads and k heads
-  const int n_rot_heads = H + Hkv;
-  for (int w = threadIdx.x; w < n_rot_heads * half; w += blockDim.x) {
+  if ((int)blockIdx.y < rot_blocks) {
+    const int w = blockIdx.y * ROPE_THREADS + threadIdx.x;
+    if (w >= (H + Hkv) * half) return;
     const int h = w / half, j = w - h * half;
-    const float ang = (float)pos * inv_freq[j];
-    float sn, cs;
-    sincosf(ang, &sn, &cs);
     const int i0 = pairing == 0 ? j : 2 * j;
     const int i1 = pairing == 0 ? j + half : 2 * j + 1;
     T* hv = row + (size_t)h * D;
     const float a = to_float(hv[i0]), b = to_float(hv[i1]);
+    const float ang = (float)pos * inv_freq[j];
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
     const T o0 = from_float<T>(a * cs - b * sn);
     const T o1 = from_float<T>(b * cs + a * sn);
     if (h < H) {
@@ -174,16 +264,22 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
       dst[i0] = o0;
       dst[i1] = o1;
     }
+    return;
   }
-  if (cache_ok) {
-    // key elements beyond the rotary width, and all value elements, are copied as they are
-    const int tail = D - rot;
-    for (int w = threadIdx.x; w < Hkv * tail; w += blockDim.x) {
-      const int h = w / tail, i = rot + (w - h * tail);
+  if (!cache_ok) return;
+  // copy blocks: all value elements, then key elements beyond the rotary width
+  const int tail = D - rot;
+  const int n_v = Hkv * D, n_tail = Hkv * tail;
+  const int stride = (gridDim.y - rot_blocks) * ROPE_THREADS;
+  const T* vrow = row + (size_t)(H + Hkv) * D;
+  for (int w = (blockIdx.y - rot_blocks) * ROPE_THREADS + threadIdx.x; w < n_v + n_tail; w += stride) {
+    if (w < n_v) {
+      vc[cache_base + w] = vrow[w];
+    } else {
+      const int u = w - n_v;
+      const int h = u / tail, i = rot + (u - h * tail);
       kc[cache_base + (size_t)h * D + i] = row[(size_t)(H + h) * D + i];
     }
-    const T* vrow = row + (size_t)(H + Hkv) * D;
-    for (int w = threadIdx.x; w < Hkv * D; w += blockDim.x) vc[cache_base + w] = vrow[w];
   }
 }
 
@@ -193,15 +289,24 @@ SB_EXPORT int sb_rope_cache_write(void* qkv, const int* positions, const int* to
                                   cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || D <= 0 || rot < 0 || rot > D || (rot & 1) || ps <= 0) return SB_ERR_SHAPE;
-  const int threads = 128;
+  const int rot_blocks = ((H + Hkv) * (rot / 2) + ROPE_THREADS - 1) / ROPE_THREADS;
+  int copy_blocks = 0;
+  if (write_cache) {
+    copy_blocks = (Hkv * (2 * D - rot) + ROPE_THREADS * 4 - 1) / (ROPE_THREADS * 4);
+    if (copy_blocks < 1) copy_blocks = 1;
+    if (copy_blocks > 64) copy_blocks = 64;
+  }
+  if (rot_blocks + copy_blocks == 0) return 0;
+  if (rot_blocks + copy_blocks > 65535) return SB_ERR_LIMIT;
+  dim3 grid(n_tokens, rot_blocks + copy_blocks);
   if (dtype == SB_DTYPE_F32)
-    rope_cache_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, positions, token_row, inv_freq, pairing, rot, H,
-                                                                     Hkv, D, (float*)kc, (float*)vc, block_table, bt_width, ps,
-                                                                     num_pages, write_cache, errors);
+    rope_cache_write_kernel<float><<<grid, ROPE_THREADS, 0, stream>>>((float*)qkv, positions, token_row, inv_freq, pairing, rot, H,
+                                                                      Hkv, D, (float*)kc, (float*)vc, block_table, bt_width, ps,
+                                                                      num_pages, write_cache, rot_blocks, errors);
   else if (dtype == SB_DTYPE_BF16)
-    rope_cache_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+    rope_cache_write_kernel<__nv_bfloat16><<<grid, ROPE_THREADS, 0, stream>>>(
         (__nv_bfloat16*)qkv, positions, token_row, inv_freq, pairing, rot, H, Hkv, D, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc,
-        block_table, bt_width, ps, num_pages, write_cache, errors);
+        block_table, bt_width, ps, num_pages, write_cache, rot_blocks, errors);
   else
     return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();

@@ -120,6 +120,14 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
             os.remove(tmp)
         raise BuildError(f"nvcc failed for {name} (exit {proc.returncode}):\n{' '.join(cmd)}\n{out}")
     os.replace(tmp, path)
+    # libraries of the same name built from older sources are of no use any more
+    folder = os.path.dirname(path)
+    for f in os.listdir(folder):
+        if f.startswith(name + "-") and f.endswith(".so") and os.path.join(folder, f) != path:
+            try:
+                os.remove(os.path.join(folder, f))
+            except OSError:
+                pass
     if verbose:
         _say(f"  {name} ready in {time.time() - t0:.1f} s")
     return path

@@ -46,7 +46,7 @@ def _stream():
 
 def core_jobs():
     return [
-        {"name": "sb_core", "sources": ["elementwise.cu"]},
+        {"name": "sb_core", "sources": ["elementwise.cu", "skinny_linear.cu"]},
         {"name": "sb_gemm", "sources": ["gemm_cublas.cu"], "libs": ["cublas"]},
     ]
 
@@ -83,6 +83,8 @@ class CudaKernels:
         self._verbose = verbose
         self._errors: Optional[torch.Tensor] = None
         self.force_simt_attention = False   # tests: run bfloat16 through the plain-arithmetic kernel
+        self.use_skinny_linear = True       # tests: False sends every product to the library
+        self._tickets = []                   # zeroed int32 buffers of the split-key merge (kept alive for graphs)
         self.launches = 0         # launches of this engine's own kernels
         self.library_calls = 0    # library matrix products
 
@@ -141,9 +143,27 @@ class CudaKernels:
         """out[M,N] = a[M,K] @ w[N,K]^T (library matrix product)."""
         if a.dtype != w.dtype or a.shape[1] != w.shape[1] or out.shape[0] != a.shape[0] or out.shape[1] != w.shape[0]:
             raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} do not fit")
+        m, n, k = a.shape[0], w.shape[0], a.shape[1]
+        if a.dtype == torch.bfloat16 and self.use_skinny_linear and self._core.sb_skinny_linear_supports(m, n, k, 0):
+            self.launches += 1
+            _check(self._core.sb_skinny_linear(_p(a), _p(w), _p(out), m, n, k, _DT[out.dtype], 0, _stream()), "skinny linear")
+            return
         self.library_calls += 1
-        _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), a.shape[0], w.shape[0], a.shape[1], _DT[a.dtype], _DT[out.dtype],
-                                    _stream()), "linear")
+        _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), m, n, k, _DT[a.dtype], _DT[out.dtype], _stream()), "linear")
+
+    def gate_up_swiglu(self, h, w_gate_up, out) -> None:
+        """out[T, I] = silu(h @ w_gate^T) * (h @ w_up^T), w_gate_up = [w_gate; w_up] of shape [2I, K]."""
+        t, inter, k = h.shape[0], out.shape[1], h.shape[1]
+        if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != k or out.shape[0] != t:
+            raise KernelError("gate_up_swiglu: shapes do not fit")
+        if h.dtype == torch.bfloat16 and self.use_skinny_linear and self._core.sb_skinny_linear_supports(t, inter, k, 1):
+            self.launches += 1
+            _check(self._core.sb_skinny_linear(_p(h), _p(w_gate_up), _p(out), t, inter, k, _DT[out.dtype], 1, _stream()),
+                   "skinny gate/up")
+            return
+        gate_up = torch.empty((t, 2 * inter), dtype=h.dtype, device=h.device)
+        self.linear(h, w_gate_up, gate_up)
+        self.swiglu(gate_up, out)
 
     def swiglu(self, gate_up, out) -> None:
         self.launches += 1
@@ -188,17 +208,25 @@ class CudaKernels:
             which |= 1
         if group <= 16 and min_q * group <= 16:
             which |= 2
-        split_size, num_splits, scratch = 64, 1, None
+        split_size, num_splits, scratch, tickets = 64, 1, None, None
         if which & 2:
             split_size, num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
             if num_splits > 1:
                 nbytes = lib.sb_attention_mma_scratch_bytes(shape.rows, kv_heads, num_splits)
                 scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
-        self.launches += (which & 1) + ((which >> 1) & 1) * (2 if num_splits > 1 else 1)
+                tickets = self._ticket_buffer(shape.rows * kv_heads)
+        self.launches += (which & 1) + ((which >> 1) & 1)
         _check(lib.sb_attention_mma(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-            which, split_size, num_splits, _p(scratch), _stream()), "attention")
+            which, split_size, num_splits, _p(scratch), _p(tickets), _stream()), "attention")
+
+    def _ticket_buffer(self, n: int) -> torch.Tensor:
+        """A zeroed int32 buffer of at least n entries. Every launch leaves it zeroed, so one buffer serves all
+        layers and steps; a larger one is made when needed and the old ones stay alive for captured graphs."""
+        if not self._tickets or self._tickets[-1].numel() < n:
+            self._tickets.append(torch.zeros(max(n, 4096), dtype=torch.int32, device=self.device))
+        return self._tickets[-1]
 
     def sample(self, logits, temperature, req_ids, tok_index, seed, out) -> None:
         self.launches += 1

@@ -41,10 +41,8 @@ class SwiGLU(FeedForward):
     def forward(self, h, ctx):
         rt = self.rt
         t = h.shape[0]
-        gate_up = rt.empty_act((t, 2 * self.intermediate))
-        rt.kernels.linear(h, self.w_gate_up, gate_up)
         act = rt.empty_act((t, self.intermediate))
-        rt.kernels.swiglu(gate_up, act)
+        rt.kernels.gate_up_swiglu(h, self.w_gate_up, act)
         out = rt.empty_act((t, self.hidden))
         rt.kernels.linear(act, self.w_down, out)
         return out

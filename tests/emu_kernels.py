@@ -52,6 +52,11 @@ class EmuKernels:
         u = gate_up[:, inter:].to(self.math)
         out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
+    def gate_up_swiglu(self, h, w_gate_up, out):
+        gate_up = torch.empty((h.shape[0], w_gate_up.shape[0]), dtype=h.dtype, device=h.device)
+        self.linear(h, w_gate_up, gate_up)
+        self.swiglu(gate_up, out)
+
     def rope_cache_write(self, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
                          k_cache, v_cache, block_table, page_size, write_cache):
         t = qkv.shape[0]

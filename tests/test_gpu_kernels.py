@@ -339,3 +339,56 @@ def test_attention_unwritten_cache_does_not_leak(K):
     E.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, 0.125, 0, ref, s["shape"])
     assert bool(torch.isfinite(out.float()).all())
     torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("n,k", [(2048, 2048), (100, 64), (331, 96), (16, 8192), (4000, 32)])
+def test_skinny_linear(K, m, n, k):
+    """The few-rows product against float64, bfloat16 and float outputs; and a row's result must not depend on
+    how many other rows there are."""
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    assert K._core.sb_skinny_linear_supports(m, n, k, 0) == 1
+    before = K.launches
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=out_dtype)
+        K.linear(a, w, out)
+        tol = dict(atol=2e-3 * math.sqrt(k / 64), rtol=1e-4) if out_dtype == torch.float32 else dict(atol=0.1 * math.sqrt(k / 64), rtol=1e-2)
+        torch.testing.assert_close(out.double(), ref, **tol)
+    assert K.launches == before + 2, "these sizes must take the hand-written kernel"
+    one = torch.empty(1, n, device=DEV)
+    K.linear(a[m - 1:m].contiguous(), w, one)
+    full = torch.empty(m, n, device=DEV)
+    K.linear(a, w, full)
+    assert torch.equal(one[0], full[m - 1])
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 16])
+@pytest.mark.parametrize("inter,k", [(8192, 2048), (200, 96), (320, 192)])
+def test_fused_gate_up_equals_unfused(K, m, inter, k):
+    h = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=DEV) * 0.05).to(torch.bfloat16)
+    fused = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    K.gate_up_swiglu(h, w, fused)
+    K.use_skinny_linear = False
+    try:
+        plain = torch.empty_like(fused)
+        K.gate_up_swiglu(h, w, plain)
+    finally:
+        K.use_skinny_linear = True
+    ref = torch.empty_like(fused)
+    E.gate_up_swiglu(h, w, ref)
+    scale = float(ref.float().abs().max())
+    torch.testing.assert_close(fused.float(), ref.float(), atol=scale * 2.0 ** -6, rtol=0)
+    torch.testing.assert_close(plain.float(), ref.float(), atol=scale * 2.0 ** -6, rtol=0)
+
+
+def test_sizes_the_skinny_kernel_leaves_to_the_library(K):
+    for m, n, k in [(33, 64, 64), (4, 64, 120), (4, 64, 16)]:
+        assert K._core.sb_skinny_linear_supports(m, n, k, 0) == 0
+        a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+        w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+        out = torch.empty(m, n, device=DEV)
+        K.linear(a, w, out)
+        torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=1e-2, rtol=1e-3)
