@@ -1,7 +1,9 @@
 """The cache manager: paged keys/values with per-request block tables, and state slots.
 
 Layout. Every execution of a mixer that asked for pages owns a pair of device
-tensors K, V of shape [num_pages, page_size, kv_heads, head_dim]. Executions
+tensors K, V of shape [num_pages, kv_heads, page_size, head_dim]
+(the tokens of one kv head lie together inside a page, so attention reads
+contiguous runs of page_size rows). Executions
 with the same geometry and window form a *group*: one pool of page ids and one
 block table per request serve all of them (page id p means page p in every
 tensor of the group), as one id serves every layer in the reference
@@ -40,7 +42,7 @@ class CacheView:
     """What one execution of a mixer sees of the cache."""
 
     group: int                 # index into StepContext.block_tables
-    k: object                  # [num_pages, page_size, kv_heads, head_dim] or None
+    k: object                  # [num_pages, kv_heads, page_size, head_dim] or None
     v: object
     page_size: int
     writes: bool               # False: reads the cache another execution wrote
@@ -107,7 +109,7 @@ class CacheManager:
                 if need is None:
                     continue
                 if need.has_pages:
-                    shape = (num_pages, page_size, need.kv_heads, need.head_dim)
+                    shape = (num_pages, need.kv_heads, page_size, need.head_dim)
                     self._kv[i] = (torch.zeros(shape, dtype=kv_dtype, device=device),
                                    torch.zeros(shape, dtype=kv_dtype, device=device))
                 if need.state_shape is not None:

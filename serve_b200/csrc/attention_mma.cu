@@ -115,8 +115,12 @@ __device__ __forceinline__ void finish_split(const Params& p, int r, int hk, int
   if (threadIdx.x == 0) p.tickets[(size_t)r * p.Hkv + hk] = 0;
 }
 
+constexpr int BT_CACHE = 512;        // block-table entries a thread block keeps in shared memory
+
 // Fetch keys [kt, kt+BN) of kv head hk into one stage of shared memory; keys outside [lo, hi) become zeros.
-__device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int hk, int kt, int lo, int hi, bf16* Ks, bf16* Vs) {
+// bt points at the table entry of block bt_first (shared memory copy, or the table itself with bt_first 0).
+__device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int bt_first, int hk, int kt, int lo, int hi, bf16* Ks,
+                                             bf16* Vs) {
 #pragma unroll
   for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += THREADS) {
     const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
@@ -125,9 +129,9 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
     size_t off = 0;
     if (ok) {
       const int blk = key / p.ps;
-      const int page = blk < p.bt_width ? bt[blk] : -1;
+      const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
-      if (ok) off = (((size_t)page * p.ps + (key - blk * p.ps)) * p.Hkv + hk) * D + ch * 8;
+      if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
     cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
@@ -135,15 +139,20 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
 }
 
 // WM warps along rows, WN warps along the keys of a tile (WM * WN == 4).
+// Stages of the key/value pipeline: decoding blocks do little arithmetic per byte and want many loads in flight.
+__host__ __device__ constexpr int stages_for(bool deep) { return deep ? (D <= 64 ? 4 : (D <= 128 ? 3 : 2)) : 2; }
+
 template <int WM, int WN>
 __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) {
   constexpr int BM = WM * 16;
   constexpr int KW = BN / WN;          // keys per warp per tile
   constexpr int NT = KW / 8;           // score n-tiles per warp
   constexpr bool DEEP = (WN > 1);
+  constexpr int NSTAGE = stages_for(DEEP);
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int bt_s[BT_CACHE];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [BM][LDS]
-  bf16* KVs = Qs + BM * LDS;                        // 2 stages x (K [BN][LDS], V [BN][LDS])
+  bf16* KVs = Qs + BM * LDS;                        // NSTAGE stages x (K [BN][LDS], V [BN][LDS])
 
   const int r = blockIdx.z, hk = blockIdx.y;
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
@@ -173,6 +182,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
   const int wm = DEEP ? 0 : warp, wn = DEEP ? warp : 0;
   const int g = lane >> 2, tq = lane & 3;
   const int* bt = p.block_table + (size_t)r * p.bt_width;
+  int bt_first = 0;
 
   if (DEEP && lo >= hi) {
     // no keys fall to this split: say so, so that the merge skips it
@@ -194,8 +204,21 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
   }
   const int kt0 = (lo / BN) * BN;
   const int n_tiles = (hi - kt0 + BN - 1) / BN;
-  load_kv_tile(p, bt, hk, kt0, lo, hi, KVs, KVs + BN * LDS);
-  cp_async_commit();
+  {
+    // the table entries of this block's keys, once, instead of a dependent global load per row and tile
+    const int b_lo = lo / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
+    if (b_hi - b_lo + 1 <= BT_CACHE) {
+      for (int i = tid; i <= b_hi - b_lo; i += THREADS) bt_s[i] = bt[b_lo + i];
+      __syncthreads();
+      bt = bt_s;
+      bt_first = b_lo;
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < NSTAGE - 1; ++s) {
+    if (s < n_tiles) load_kv_tile(p, bt, bt_first, hk, kt0 + s * BN, lo, hi, KVs + s * 2 * BN * LDS, KVs + s * 2 * BN * LDS + BN * LDS);
+    cp_async_commit();
+  }
 
   // positions of this thread's two rows (g and g+8 of the warp's 16)
   const int row_a = m0 + wm * 16 + g, row_b = row_a + 8;
@@ -208,15 +231,17 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
 
   for (int it = 0; it < n_tiles; ++it) {
     const int kt = kt0 + it * BN;
-    bf16* Ks = KVs + (it & 1) * 2 * BN * LDS;
+    bf16* Ks = KVs + (it % NSTAGE) * 2 * BN * LDS;
     bf16* Vs = Ks + BN * LDS;
-    if (it + 1 < n_tiles) {
-      bf16* Kn = KVs + ((it + 1) & 1) * 2 * BN * LDS;
-      load_kv_tile(p, bt, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    {
+      // fetch NSTAGE-1 tiles ahead, into the stage the previous iteration has finished with
+      const int nx = it + NSTAGE - 1;
+      if (nx < n_tiles) {
+        bf16* Kn = KVs + (nx % NSTAGE) * 2 * BN * LDS;
+        load_kv_tile(p, bt, bt_first, hk, kt0 + nx * BN, lo, hi, Kn, Kn + BN * LDS);
+      }
+      cp_async_commit();           // an empty group when nothing was fetched: the count below stays right
+      cp_async_wait<NSTAGE - 1>();  // tile ``it`` (and the queries) have landed
     }
     __syncthreads();
 
@@ -362,6 +387,307 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
   }
 }
 
+// The deep shape, for requests with at most 16 rows (decoding). grid (splits, Hkv, R), 4 warps. The keys of the
+// block's split are dealt to the warps in sub-tiles of DKW (warp w takes sub-tiles w, w+4, ...); every warp runs
+// a cp.async pipeline of its own over private shared memory, so no block-wide barrier sits in the loop and
+// the warps hide one another's latencies. The four partial results meet in shared memory at the end.
+// The loop is written for few instructions per byte: a sub-tile lies in one page whenever the page size is a
+// multiple of DKW (one table lookup, contiguous source rows); tiles away from the edges of the key range skip
+// the mask; rows 8..15 of the tile are only computed when the request has that many (UPPER).
+constexpr int DKW = D <= 64 ? 32 : 16;                    // keys per warp per step
+constexpr int DNT = DKW / 8;                              // score n-tiles per step
+constexpr int DSTAGES = D <= 128 ? 3 : 2;                 // steps in flight per warp
+constexpr bool DQ_IN_REGS = D <= 128;                     // query fragments live in registers
+constexpr int DCOPIES = DKW * CHUNKS / 32;                // 16-byte copies per lane per sub-tile and tensor
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Sub-tile of keys [k0, k0 + DKW) of kv head hk -> one stage. Keys outside [lo, hi) become zeros.
+__device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, int bt_first, int hk, int k0, int lo, int hi,
+                                                bool same_page, bf16* Ks, bf16* Vs, int lane) {
+  if (same_page) {
+    const int blk = k0 / p.ps;
+    const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
+    const bool page_ok = page >= 0 && page < p.num_pages;
+    const size_t base = (((size_t)(page_ok ? page : 0) * p.Hkv + hk) * p.ps + (k0 - blk * p.ps)) * D;
+    const bool inner = page_ok && k0 >= lo && k0 + DKW <= hi;
+#pragma unroll
+    for (int i = 0; i < DCOPIES; ++i) {
+      const int c = lane + 32 * i;
+      const int row = c / CHUNKS, ch = c - row * CHUNKS;
+      const bool ok = inner || (page_ok && k0 + row >= lo && k0 + row < hi);
+      cp_async16(Ks + row * LDS + ch * 8, p.kc + base + (size_t)c * 8, ok);
+      cp_async16(Vs + row * LDS + ch * 8, p.vc + base + (size_t)c * 8, ok);
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < DCOPIES; ++i) {
+    const int c = lane + 32 * i;
+    const int row = c / CHUNKS, ch = c - row * CHUNKS;
+    const int key = k0 + row;
+    bool ok = key >= lo && key < hi;
+    size_t off = 0;
+    if (ok) {
+      const int blk = key / p.ps;
+      const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
+      ok = page >= 0 && page < p.num_pages;
+      if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;
+    }
+    cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
+    cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+  }
+}
+
+template <bool UPPER>
+__global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int bt_s[BT_CACHE];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][LDS]
+  bf16* KVs = Qs + 16 * LDS;                                    // [4 warps][DSTAGES][K DKWxLDS, V DKWxLDS]
+
+  const int r = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
+  const int G = p.G;
+  const int M = qn * G;
+  if (M > 16 || M <= 0) return;                                 // the wide shape takes this request
+  if (UPPER != (M > 8)) return;                                 // the other instantiation takes this request
+  const int L = p.kv_len[r];
+  const int p0 = L - qn;
+  int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
+  int hi = p0 + (M - 1) / G + 1;
+  lo = max(lo, split * p.split_size);
+  hi = min(hi, (split + 1) * p.split_size);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, tq = lane & 3;
+  const int* bt = p.block_table + (size_t)r * p.bt_width;
+  int bt_first = 0;
+
+  if (lo >= hi) {
+    if (tid < 16) {
+      float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
+      ml[0] = -INFINITY; ml[1] = 0.f;
+    }
+    if (p.num_splits > 1) finish_split(p, r, hk, q0, M);
+    return;
+  }
+  for (int idx = tid; idx < 16 * CHUNKS; idx += THREADS) {
+    const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
+    const bool ok = row < M;
+    const int tok = ok ? row / G : 0, hd = ok ? hk * G + (row - tok * G) : 0;
+    cp_async16(Qs + row * LDS + ch * 8, p.qkv + (size_t)(q0 + tok) * p.q_stride + (size_t)hd * D + ch * 8, ok);
+  }
+  cp_async_commit();
+  {
+    const int b_lo = lo / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
+    if (b_hi - b_lo + 1 <= BT_CACHE) {
+      for (int i = tid; i <= b_hi - b_lo; i += THREADS) bt_s[i] = bt[b_lo + i];
+      bt = bt_s;
+      bt_first = b_lo;
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();                                              // queries and table entries are in shared memory
+
+  const bool same_page = (p.ps % DKW) == 0;
+  const int k_first = (lo / DKW) * DKW;
+  const int n_sub = (hi - k_first + DKW - 1) / DKW;             // sub-tiles of the split
+  const int my_n = (n_sub - warp + 3) / 4;                      // this warp's share: sub-tiles warp, warp+4, ...
+  bf16* myKV = KVs + (size_t)warp * DSTAGES * 2 * DKW * LDS;
+#pragma unroll
+  for (int s = 0; s < DSTAGES - 1; ++s) {
+    if (s < my_n) load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + 4 * s) * DKW, lo, hi, same_page, myKV + s * 2 * DKW * LDS,
+                                  myKV + s * 2 * DKW * LDS + DKW * LDS, lane);
+    cp_async_commit();
+  }
+  uint32_t qf[DQ_IN_REGS ? D / 16 : 1][4];
+  if (DQ_IN_REGS) {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+      ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], Qs + (lane & 15) * LDS + kk * 16 + (lane >> 4) * 8);
+  }
+  const int pos_a = g < M ? p0 + g / G : -1;
+  const int pos_b = (UPPER && g + 8 < M) ? p0 + (g + 8) / G : -1;
+  // a sub-tile all of whose keys every row may see needs no mask: keys in [free_lo, free_hi)
+  const int free_lo = max(lo, p.window > 0 ? p0 + (M - 1) / G - p.window + 1 : 0);
+  const int free_hi = min(hi, p0 + 1);
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+  for (int it = 0; it < my_n; ++it) {
+    {
+      const int nx = it + DSTAGES - 1;
+      if (nx < my_n) {
+        bf16* Kn = myKV + (nx % DSTAGES) * 2 * DKW * LDS;
+        load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + 4 * nx) * DKW, lo, hi, same_page, Kn, Kn + DKW * LDS, lane);
+      }
+      cp_async_commit();
+      cp_async_wait<DSTAGES - 1>();
+    }
+    __syncwarp();
+    const bf16* Ks = myKV + (it % DSTAGES) * 2 * DKW * LDS;
+    const bf16* Vs = Ks + DKW * LDS;
+    const int kbase = k_first + (warp + 4 * it) * DKW;
+    float s[DNT][4];
+#pragma unroll
+    for (int j = 0; j < DNT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t a0, a1, a2, a3;
+      if (DQ_IN_REGS) {
+        a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3];
+      } else {
+        ldmatrix_x4(a0, a1, a2, a3, Qs + (lane & 15) * LDS + kk * 16 + (lane >> 4) * 8);
+      }
+#pragma unroll
+      for (int j = 0; j < DNT; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, Ks + (j * 8 + (lane >> 4) * 8 + (lane & 7)) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[j], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[j + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    // (rows beyond M hold zero queries; what they compute is finite and never stored)
+    const bool unmasked = kbase >= free_lo && kbase + DKW <= free_hi;
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+    if (unmasked) {
+#pragma unroll
+      for (int j = 0; j < DNT; ++j) {
+        s[j][0] *= p.scale_log2; s[j][1] *= p.scale_log2;
+        mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
+        if (UPPER) {
+          s[j][2] *= p.scale_log2; s[j][3] *= p.scale_log2;
+          mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < DNT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = kbase + j * 8 + tq * 2 + e;
+          const bool in_range = key >= lo && key < hi;
+          const bool ok_a = in_range && key <= pos_a && (p.window <= 0 || key > pos_a - p.window);
+          s[j][e] = ok_a ? s[j][e] * p.scale_log2 : -INFINITY;
+          mx_a = fmaxf(mx_a, s[j][e]);
+          if (UPPER) {
+            const bool ok_b = in_range && key <= pos_b && (p.window <= 0 || key > pos_b - p.window);
+            s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+            mx_b = fmaxf(mx_b, s[j][2 + e]);
+          }
+        }
+      }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    const float mn_a = fmaxf(m_a, mx_a);
+    const float use_a = (mn_a == -INFINITY) ? 0.f : mn_a;       // ex2(-inf - 0) = 0: masked entries vanish by themselves
+    const float al_a = ex2(m_a - use_a);
+    m_a = mn_a;
+    float mn_b = m_b, use_b = 0.f, al_b = 1.f;
+    if (UPPER) {
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      mn_b = fmaxf(m_b, mx_b);
+      use_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+      al_b = ex2(m_b - use_b);
+      m_b = mn_b;
+    }
+    uint32_t pa[DNT][2];
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int j = 0; j < DNT; ++j) {
+      const float p0_ = ex2(s[j][0] - use_a), p1_ = ex2(s[j][1] - use_a);
+      sum_a += p0_ + p1_;
+      pa[j][0] = pack_bf16(p0_, p1_);
+      if (UPPER) {
+        const float p2_ = ex2(s[j][2] - use_b), p3_ = ex2(s[j][3] - use_b);
+        sum_b += p2_ + p3_;
+        pa[j][1] = pack_bf16(p2_, p3_);
+      } else {
+        pa[j][1] = 0u;
+      }
+    }
+    l_a = l_a * al_a + sum_a;
+    if (UPPER) l_b = l_b * al_b + sum_b;
+    // rescale the output only when some row's maximum moved (warp-uniform decision)
+    if (__any_sync(0xffffffffu, al_a != 1.f || al_b != 1.f)) {
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= al_a; o[i][1] *= al_a;
+        if (UPPER) { o[i][2] *= al_b; o[i][3] *= al_b; }
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < DKW / 16; ++ks) {
+#pragma unroll
+      for (int i = 0; i < D / 8; i += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, Vs + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + i * 8 + (lane >> 4) * 8);
+        mma_bf16(o[i], pa[2 * ks][0], pa[2 * ks][1], pa[2 * ks + 1][0], pa[2 * ks + 1][1], b0, b1);
+        mma_bf16(o[i + 1], pa[2 * ks][0], pa[2 * ks][1], pa[2 * ks + 1][0], pa[2 * ks + 1][1], b2, b3);
+      }
+    }
+    __syncwarp();   // all lanes have read this stage before a later fetch overwrites it
+  }
+  cp_async_wait<0>();
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  __syncthreads();                                              // every warp is done with its stages: reuse the memory
+  float* Om = reinterpret_cast<float*>(smem_raw);               // [4][16][D]
+  float* MLm = Om + 4 * 16 * D;                                 // [4][16][2]
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    float* d0 = Om + ((size_t)warp * 16 + g) * D + i * 8 + tq * 2;
+    float* d1 = Om + ((size_t)warp * 16 + g + 8) * D + i * 8 + tq * 2;
+    d0[0] = o[i][0]; d0[1] = o[i][1];
+    d1[0] = o[i][2]; d1[1] = o[i][3];
+  }
+  if (tq == 0) {
+    MLm[(warp * 16 + g) * 2] = m_a;      MLm[(warp * 16 + g) * 2 + 1] = l_a;
+    MLm[(warp * 16 + g + 8) * 2] = m_b;  MLm[(warp * 16 + g + 8) * 2 + 1] = l_b;
+  }
+  __syncthreads();
+  const bool last = p.num_splits == 1;
+  for (int idx = tid; idx < M * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, MLm[(w * 16 + row) * 2]);
+    float ll = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = MLm[(w * 16 + row) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+      ll += MLm[(w * 16 + row) * 2 + 1] * f;
+      acc += Om[((size_t)w * 16 + row) * D + d] * f;
+    }
+    if (last) {
+      const int tok = row / G, hd = hk * G + (row - tok * G);
+      p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    } else {
+      const size_t base = (((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + row;
+      p.part_o[base * D + d] = acc;
+      if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
+    }
+  }
+  if (!last) finish_split(p, r, hk, q0, M);
+}
+
+size_t deep_smem_bytes() {
+  const size_t tiles = (size_t)(16 + 4 * DSTAGES * 2 * DKW) * LDS * sizeof(bf16);
+  const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+  return tiles > merge ? tiles : merge;
+}
+
 // Merge the partial results of the key splits of the deep shape. grid (Hkv, R), 128 threads.
 __global__ void __launch_bounds__(THREADS) attention_merge_kernel(const Params p) {
   const int r = blockIdx.y, hk = blockIdx.x;
@@ -372,7 +698,7 @@ __global__ void __launch_bounds__(THREADS) attention_merge_kernel(const Params p
 }
 
 template <int WM, int WN> size_t smem_bytes() {
-  const size_t tiles = (size_t)(WM * 16 + 4 * BN) * LDS * sizeof(bf16);
+  const size_t tiles = (size_t)(WM * 16 + stages_for(WN > 1) * 2 * BN) * LDS * sizeof(bf16);
   const size_t merge = WN > 1 ? (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float) : 0;
   return tiles > merge ? tiles : merge;
 }
@@ -422,11 +748,18 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
       p.part_ml = p.part_o + (size_t)n_rows * Hkv * num_splits * 16 * D;
       p.tickets = tickets;
     }
-    auto k = attention_mma_kernel<1, 4>;
-    const size_t smem = smem_bytes<1, 4>();
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<dim3(num_splits, Hkv, n_rows), THREADS, smem, stream>>>(p);
+    const size_t smem = deep_smem_bytes();
+    // bit 2 of ``which``: some request has more than 8 rows (the caller knows the largest token count)
+    auto k_lower = attention_deep_kernel<false>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k_lower, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k_lower<<<dim3(num_splits, Hkv, n_rows), THREADS, smem, stream>>>(p);
     SB_LAUNCH_CHECK();
+    if (which & 4) {
+      auto k_upper = attention_deep_kernel<true>;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(k_upper, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      k_upper<<<dim3(num_splits, Hkv, n_rows), THREADS, smem, stream>>>(p);
+      SB_LAUNCH_CHECK();
+    }
     if (num_splits > 1 && tickets == nullptr) {
       attention_merge_kernel<<<dim3(Hkv, n_rows), THREADS, 0, stream>>>(p);
       SB_LAUNCH_CHECK();

@@ -28,7 +28,7 @@ static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head_dim must be a multiple o
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
-    const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,
+    const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,  // caches [P, Hkv, ps, D]
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
     int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out) {
   extern __shared__ float smem[];
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
         const int blk = key / ps;
         const int page = blk < bt_width ? bt[blk] : -1;
         if (page >= 0 && page < num_pages) {
-          const size_t off = (((size_t)page * ps + (key - blk * ps)) * Hkv + hk) * D + d;
+          const size_t off = (((size_t)page * Hkv + hk) * ps + (key - blk * ps)) * D + d;
           kvv = to_float(kc[off]);
           vvv = to_float(vc[off]);
         }

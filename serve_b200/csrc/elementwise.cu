@@ -216,7 +216,7 @@ SB_EXPORT int sb_swiglu(const void* gate_up, void* out, int n_tokens, int inter,
 // ------------------------------------------------------ rotary + cache write
 // qkv: [T, (H + 2*Hkv) * D]. Queries and keys are rotated (angle = position *
 // inv_freq[j], float); queries in place, rotated keys and plain values go to
-// the request's pages: cache[page, pos % ps, kv_head, :], page =
+// the request's pages: cache[page, kv_head, pos % ps, :], page =
 // block_table[row, pos / ps]. pairing 0: pairs (j, j + rot/2); 1: (2j, 2j+1).
 // A page id < 0 or a block index beyond the table is counted in *errors and
 // the write is skipped.
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(ROPE_THREADS) rope_cache_write_kernel(
     const int page = (blk < bt_width && pos >= 0) ? block_table[(size_t)r * bt_width + blk] : -1;
     cache_ok = page >= 0 && page < num_pages;
     if (!cache_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicAdd(errors, 1);
-    cache_base = ((size_t)(cache_ok ? page : 0) * ps + (pos % ps)) * Hkv * D;
+    cache_base = (size_t)(cache_ok ? page : 0) * Hkv * ps * D + (size_t)(pos % ps) * D;   // + kv_head * ps * D
   }
   if ((int)blockIdx.y < rot_blocks) {
     const int w = blockIdx.y * ROPE_THREADS + threadIdx.x;
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(ROPE_THREADS) rope_cache_write_kernel(
       hv[i0] = o0;
       hv[i1] = o1;
     } else if (cache_ok) {
-      T* dst = kc + cache_base + (size_t)(h - H) * D;
+      T* dst = kc + cache_base + (size_t)(h - H) * ps * D;
       dst[i0] = o0;
       dst[i1] = o1;
     }
@@ -274,11 +274,12 @@ __global__ void __launch_bounds__(ROPE_THREADS) rope_cache_write_kernel(
   const T* vrow = row + (size_t)(H + Hkv) * D;
   for (int w = (blockIdx.y - rot_blocks) * ROPE_THREADS + threadIdx.x; w < n_v + n_tail; w += stride) {
     if (w < n_v) {
-      vc[cache_base + w] = vrow[w];
+      const int h = w / D, i = w - h * D;
+      vc[cache_base + (size_t)h * ps * D + i] = vrow[w];
     } else {
       const int u = w - n_v;
       const int h = u / tail, i = rot + (u - h * tail);
-      kc[cache_base + (size_t)h * D + i] = row[(size_t)(H + h) * D + i];
+      kc[cache_base + (size_t)h * ps * D + i] = row[(size_t)(H + h) * D + i];
     }
   }
 }

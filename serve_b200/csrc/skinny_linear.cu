@@ -3,12 +3,11 @@
 // leaves this to cuBLAS (nn.Linear, serve/model.py:95-97,80-82,159), whose kernels for such shapes do not
 // fill the memory system at N = 2048.
 //
-// Roles are swapped on the tensor cores (mma.sync m16n8k16): 16 rows of w are the 16-row operand, the
-// M activation rows the 8-column operand. A block of 8 warps owns 16 output columns and splits K eight
-// ways; partial sums meet in shared memory and are added in a fixed order, so a row's result does not
-// depend on how many other rows the step has. Each thread fetches 16 contiguous bytes of a w row per 32
-// k-values straight into registers; both operands use the same permutation of k inside such a group of
-// 32, which a dot product does not notice.
+// On the tensor cores (mma.sync m16n8k16) the activation rows are the 16-row operand and 8 rows of w the
+// 8-column operand. A block of 8 warps owns 8 output columns and splits K eight ways; partial sums meet in
+// shared memory and are added in a fixed order, so a row's result does not depend on how many other rows the
+// step has. Each thread fetches 16 contiguous bytes of a w row per 32 k-values straight into registers; both
+// operands use the same permutation of k inside such a group of 32, which a dot product does not notice.
 //
 // With gate_up set, w is [2*N, K] (gate rows, then up rows) and the block also owns rows N + n of it:
 // out[m, n] = silu(gate) * up  (serve/model.py:85), saving a pass over the [M, 2N] intermediate.
@@ -21,7 +20,7 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int UNROLL = 4;   // groups of 32 k-values whose loads are issued together
+constexpr int BN = 8;       // output columns per block
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 v;
@@ -38,35 +37,35 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// MT: tiles of 8 activation rows (M <= 8*MT). GU: fused gate/up with SwiGLU epilogue. OutT: bf16 or float.
-template <int MT, bool GU, typename OutT>
-__global__ void __launch_bounds__(THREADS) skinny_linear_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w,
+// MT: tiles of 16 activation rows (M <= 16*MT); HALF: only rows 0..7 of the single tile exist (M <= 8).
+// GU: fused gate/up with SwiGLU epilogue. OutT: bf16 or float.
+template <int MT, bool HALF, bool GU, typename OutT>
+__global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w,
                                                                 OutT* __restrict__ out, int M, int N, int K) {
   constexpr int NW = GU ? 2 : 1;
-  __shared__ float red[WARPS][NW][MT][16 * 8];
+  constexpr int UNROLL = (MT * NW > 1) ? 4 : 8;   // groups of 32 k-values whose loads are issued together
+  __shared__ float red[WARPS][NW][MT][16 * BN];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, tq = lane & 3;
-  const int n0 = blockIdx.x * 16;
+  const int n0 = blockIdx.x * BN;
   // this warp's share of K, in groups of 32
   const int groups = K / 32;
   const int per = (groups + WARPS - 1) / WARPS;
   const int g_lo = warp * per, g_hi = min(groups, g_lo + per);
 
-  const int ra = min(n0 + g, N - 1), rb = min(n0 + g + 8, N - 1);   // clamped: rows beyond N are computed and dropped
-  const bf16* wa[NW];
-  const bf16* wb[NW];
-  wa[0] = w + (size_t)ra * K + tq * 8;
-  wb[0] = w + (size_t)rb * K + tq * 8;
-  if (GU) {
-    wa[1] = w + (size_t)(N + ra) * K + tq * 8;
-    wb[1] = w + (size_t)(N + rb) * K + tq * 8;
-  }
-  const bf16* xa[MT];
-  bool x_ok[MT];
+  const int rn = min(n0 + g, N - 1);   // clamped: columns beyond N are computed and dropped
+  const bf16* wp[NW];
+  wp[0] = w + (size_t)rn * K + tq * 8;
+  if (GU) wp[1] = w + (size_t)(N + rn) * K + tq * 8;
+  const bf16* xg[MT];
+  const bf16* xh[MT];
+  bool okg[MT], okh[MT];
 #pragma unroll
   for (int t = 0; t < MT; ++t) {
-    x_ok[t] = t * 8 + g < M;
-    xa[t] = a + (size_t)(x_ok[t] ? t * 8 + g : 0) * K + tq * 8;
+    okg[t] = t * 16 + g < M;
+    okh[t] = !HALF && (t * 16 + g + 8 < M);
+    xg[t] = a + (size_t)(okg[t] ? t * 16 + g : 0) * K + tq * 8;
+    xh[t] = a + (size_t)(okh[t] ? t * 16 + g + 8 : 0) * K + tq * 8;
   }
 
   float c[NW][MT][4];
@@ -75,21 +74,28 @@ __global__ void __launch_bounds__(THREADS) skinny_linear_kernel(const bf16* __re
 #pragma unroll
     for (int t = 0; t < MT; ++t) c[u][t][0] = c[u][t][1] = c[u][t][2] = c[u][t][3] = 0.f;
 
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   for (int gi = g_lo; gi < g_hi; gi += UNROLL) {
-    uint4 va[UNROLL][NW], vb[UNROLL][NW], vx[UNROLL][MT];
+    uint4 vw[UNROLL][NW], vg[UNROLL][MT], vh[UNROLL][MT];
 #pragma unroll
     for (int j = 0; j < UNROLL; ++j) {
       const bool in = gi + j < g_hi;
       const size_t off = (size_t)(in ? gi + j : g_lo) * 32;
 #pragma unroll
-      for (int u = 0; u < NW; ++u) {
-        va[j][u] = ld_stream(wa[u] + off);
-        vb[j][u] = ld_stream(wb[u] + off);
-      }
+      for (int u = 0; u < NW; ++u) vw[j][u] = ld_stream(wp[u] + off);
 #pragma unroll
       for (int t = 0; t < MT; ++t) {
-        vx[j][t] = ld_cached(xa[t] + off);
-        if (!in || !x_ok[t]) vx[j][t] = make_uint4(0u, 0u, 0u, 0u);
+        vg[j][t] = ld_cached(xg[t] + off);       // always a valid address; masked below
+        if (!HALF) vh[j][t] = ld_cached(xh[t] + off);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < UNROLL; ++j) {
+      const bool in = gi + j < g_hi;
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        if (!(in && okg[t])) vg[j][t] = zero;
+        if (HALF || !(in && okh[t])) vh[j][t] = zero;
       }
     }
 #pragma unroll
@@ -98,35 +104,36 @@ __global__ void __launch_bounds__(THREADS) skinny_linear_kernel(const bf16* __re
       for (int u = 0; u < NW; ++u) {
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
-          mma_bf16(c[u][t], va[j][u].x, vb[j][u].x, va[j][u].y, vb[j][u].y, vx[j][t].x, vx[j][t].y);
-          mma_bf16(c[u][t], va[j][u].z, vb[j][u].z, va[j][u].w, vb[j][u].w, vx[j][t].z, vx[j][t].w);
+          mma_bf16(c[u][t], vg[j][t].x, vh[j][t].x, vg[j][t].y, vh[j][t].y, vw[j][u].x, vw[j][u].y);
+          mma_bf16(c[u][t], vg[j][t].z, vh[j][t].z, vg[j][t].w, vh[j][t].w, vw[j][u].z, vw[j][u].w);
         }
       }
     }
   }
-  // partial sums of the 8 warps -> shared memory; element (n_local, m_local) at n_local*8 + m_local
+  // partial sums of the 8 warps -> shared memory; element (m_local, n_local) at m_local*BN + n_local
 #pragma unroll
   for (int u = 0; u < NW; ++u)
 #pragma unroll
     for (int t = 0; t < MT; ++t) {
       float* r = red[warp][u][t];
-      r[g * 8 + tq * 2] = c[u][t][0];
-      r[g * 8 + tq * 2 + 1] = c[u][t][1];
-      r[(g + 8) * 8 + tq * 2] = c[u][t][2];
-      r[(g + 8) * 8 + tq * 2 + 1] = c[u][t][3];
+      r[g * BN + tq * 2] = c[u][t][0];
+      r[g * BN + tq * 2 + 1] = c[u][t][1];
+      if (!HALF) {
+        r[(g + 8) * BN + tq * 2] = c[u][t][2];
+        r[(g + 8) * BN + tq * 2 + 1] = c[u][t][3];
+      }
     }
   __syncthreads();
-  // 16 columns x 8*MT rows of output; thread -> (m, n_local) with n fastest so that stores are contiguous
-  for (int idx = tid; idx < MT * 8 * 16; idx += THREADS) {
-    const int m = idx >> 4, nl = idx & 15;
+  for (int idx = tid; idx < MT * 16 * BN; idx += THREADS) {
+    const int m = idx / BN, nl = idx - m * BN;
     const int n = n0 + nl;
     if (m >= M || n >= N) continue;
-    const int t = m >> 3, ml = m & 7;
+    const int t = m >> 4, ml = m & 15;
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int wv = 0; wv < WARPS; ++wv) {
-      s0 += red[wv][0][t][nl * 8 + ml];
-      if (GU) s1 += red[wv][NW - 1][t][nl * 8 + ml];
+      s0 += red[wv][0][t][ml * BN + nl];
+      if (GU) s1 += red[wv][NW - 1][t][ml * BN + nl];
     }
     float v = s0;
     if (GU) {
@@ -138,18 +145,18 @@ __global__ void __launch_bounds__(THREADS) skinny_linear_kernel(const bf16* __re
   }
 }
 
-template <int MT, bool GU, typename OutT>
+template <int MT, bool HALF, bool GU, typename OutT>
 int launch(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
-  skinny_linear_kernel<MT, GU, OutT><<<(N + 15) / 16, THREADS, 0, stream>>>((const bf16*)a, (const bf16*)w, (OutT*)out, M, N, K);
+  skinny_linear_kernel<MT, HALF, GU, OutT><<<(N + BN - 1) / BN, THREADS, 0, stream>>>((const bf16*)a, (const bf16*)w, (OutT*)out, M, N, K);
   SB_LAUNCH_CHECK();
   return 0;
 }
 
 template <bool GU, typename OutT>
 int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
-  if (M <= 8) return launch<1, GU, OutT>(a, w, out, M, N, K, stream);
-  if (M <= 16) return launch<2, GU, OutT>(a, w, out, M, N, K, stream);
-  return launch<4, GU, OutT>(a, w, out, M, N, K, stream);
+  if (M <= 8) return launch<1, true, GU, OutT>(a, w, out, M, N, K, stream);
+  if (M <= 16 || GU) return launch<1, false, GU, OutT>(a, w, out, M, N, K, stream);
+  return launch<2, false, GU, OutT>(a, w, out, M, N, K, stream);
 }
 
 }  // namespace

@@ -87,7 +87,7 @@ class Stepper:
         self._events: List[object] = [None, None]
         self._turn = 0
         self._dev: Optional[torch.Tensor] = None
-        self._graphs: Dict[int, object] = {}
+        self._graphs: Dict[tuple, object] = {}
         self.launched_graphs = 0
         self.last_h2d_bytes = 0
 
@@ -205,7 +205,7 @@ class Stepper:
             rids=rids,
         )
         if graphable:
-            logits = self._run_graph(ctx, r)
+            logits = self._run_graph(ctx, r, max(new_lens))
         else:
             logits = self.model.forward(ctx, self.views)
         for rid, n in batch:
@@ -213,16 +213,20 @@ class Stepper:
         return logits
 
     # ---- CUDA graphs for pure-decode steps ------------------------------------
-    def _run_graph(self, ctx: StepContext, r: int):
+    def _run_graph(self, ctx: StepContext, r: int, longest: int):
         """Replay (capturing on first use) the decode step for ``r`` requests.
 
-        The packed buffer has the same layout and address for a given r, grids
-        are sized from the context limit rather than from this batch's lengths,
-        so one captured graph serves every decode step of that batch size.
+        The packed buffer has the same layout and address for a given r, and grids
+        are sized from a length class (the next power of two above the longest
+        sequence, at least 1024, at most the context limit) rather than from this
+        batch's lengths, so one captured graph serves every decode step of that
+        batch size until a sequence grows into the next class.
         """
-        g = self._graphs.get(r)
+        bucket = min(self.cache.max_context, max(1024, 1 << (longest - 1).bit_length()))
+        key = (r, bucket)
+        g = self._graphs.get(key)
         if g is None:
-            shape = BatchShape(r, r, 1, 1, self.cache.max_context, True)
+            shape = BatchShape(r, r, 1, 1, bucket, True)
             static_ctx = StepContext(**{**ctx.__dict__, "shape": shape})
             # warm up outside capture (allocator pools, cuBLAS workspaces, lazy module loads)
             s = torch.cuda.Stream(device=self.rt.device)
@@ -237,12 +241,12 @@ class Stepper:
                 out = self.model.forward(static_ctx, self.views)
             counts = (getattr(k, "launches", 0) - before[0], getattr(k, "library_calls", 0) - before[1])
             g = (graph, out, self._dev, counts)
-            self._graphs[r] = g
+            self._graphs[key] = g
         graph, out, dev, counts = g
         if dev is not self._dev:
             # the packed buffer was re-made larger since capture: capture again
-            del self._graphs[r]
-            return self._run_graph(ctx, r)
+            del self._graphs[key]
+            return self._run_graph(ctx, r, longest)
         graph.replay()
         self.launched_graphs += 1
         k = self.rt.kernels

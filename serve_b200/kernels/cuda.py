@@ -191,12 +191,12 @@ class CudaKernels:
             _DT[qkv.dtype], _stream()), "attention")
 
     # Blocks the deep shape aims at: a few per SM, so that key splits fill the 148 SMs at small batches.
-    TARGET_BLOCKS = 148 * 4
+    TARGET_BLOCKS = 148 * 8
 
     def split_plan(self, rows: int, kv_heads: int, max_kv: int):
         """(split_size, num_splits) of the deep shape for a batch; a function of sizes only, never of data."""
         want = max(1, self.TARGET_BLOCKS // max(1, rows * kv_heads))
-        split_size = max(128, -(-(-(-max_kv // want)) // 64) * 64)
+        split_size = max(256, -(-(-(-max_kv // want)) // 64) * 64)
         return split_size, max(1, -(-max_kv // split_size))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
@@ -208,6 +208,8 @@ class CudaKernels:
             which |= 1
         if group <= 16 and min_q * group <= 16:
             which |= 2
+            if group > 8 or (shape.max_q > 1 and min(shape.max_q, 16 // group) * group > 8):
+                which |= 4      # some request of the deep shape may have more than 8 rows
         split_size, num_splits, scratch, tickets = 64, 1, None, None
         if which & 2:
             split_size, num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
@@ -215,7 +217,7 @@ class CudaKernels:
                 nbytes = lib.sb_attention_mma_scratch_bytes(shape.rows, kv_heads, num_splits)
                 scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
-        self.launches += (which & 1) + ((which >> 1) & 1)
+        self.launches += (which & 1) + ((which >> 1) & 1) + ((which >> 2) & 1)
         _check(lib.sb_attention_mma(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,

@@ -79,8 +79,8 @@ class EmuKernels:
             pos = positions.long()
             pages = block_table.long()[token_row.long(), pos // page_size]
             assert bool((pages >= 0).all()), "cache write to a missing page"
-            k_cache[pages, pos % page_size] = qk[:, heads:]
-            v_cache[pages, pos % page_size] = x[:, heads + kv_heads:]
+            k_cache[pages, :, pos % page_size] = qk[:, heads:]          # caches are [pages, kv_heads, page_size, D]
+            v_cache[pages, :, pos % page_size] = x[:, heads + kv_heads:]
 
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
                   page_size, scale, window, out, shape):
@@ -98,8 +98,8 @@ class EmuKernels:
             lo = max(0, (L - n) - window + 1) if window else 0
             pages = block_table[r].long()[key_pos[lo:] // page_size]
             assert bool((pages >= 0).all()), "attention reads a missing page"
-            k = k_cache[pages, key_pos[lo:] % page_size].to(self.math)
-            v = v_cache[pages, key_pos[lo:] % page_size].to(self.math)
+            k = k_cache[pages, :, key_pos[lo:] % page_size].to(self.math)
+            v = v_cache[pages, :, key_pos[lo:] % page_size].to(self.math)
             kk, vv = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
             s = torch.einsum("thd,shd->hts", q, kk) * scale
             qp = torch.arange(L - n, L, device=qkv.device)[:, None]
