@@ -460,14 +460,22 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
   const int p0 = L - qn;
   int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
   int hi = p0 + (M - 1) / G + 1;
-  lo = max(lo, split * p.split_size);
-  hi = min(hi, (split + 1) * p.split_size);
+  {
+    // the request's keys are shared out evenly over the launch's splits, in units of one step of all four warps
+    constexpr int UNIT = 4 * DKW;
+    const int split_size = max(UNIT, ((hi - lo + p.num_splits - 1) / p.num_splits + UNIT - 1) / UNIT * UNIT);
+    const int base = (lo / UNIT) * UNIT;
+    lo = max(lo, base + split * split_size);
+    hi = min(hi, base + (split + 1) * split_size);
+  }
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, tq = lane & 3;
   const int* bt = p.block_table + (size_t)r * p.bt_width;
   int bt_first = 0;
 
   if (lo >= hi) {
+    pdl_launch_dependents();
+    pdl_wait();
     if (tid < 16) {
       float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
       ml[0] = -INFINITY; ml[1] = 0.f;
@@ -475,14 +483,8 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
     if (p.num_splits > 1) finish_split(p, r, hk, q0, M);
     return;
   }
-  for (int idx = tid; idx < 16 * CHUNKS; idx += THREADS) {
-    const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
-    const bool ok = row < M;
-    const int tok = ok ? row / G : 0, hd = ok ? hk * G + (row - tok * G) : 0;
-    cp_async16(Qs + row * LDS + ch * 8, p.qkv + (size_t)(q0 + tok) * p.q_stride + (size_t)hd * D + ch * 8, ok);
-  }
-  cp_async_commit();
   {
+    // lengths and block tables are the step's own inputs: fetched while the kernel before this one finishes
     const int b_lo = lo / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
     if (b_hi - b_lo + 1 <= BT_CACHE) {
       for (int i = tid; i <= b_hi - b_lo; i += THREADS) bt_s[i] = bt[b_lo + i];
@@ -490,6 +492,15 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
       bt_first = b_lo;
     }
   }
+  pdl_launch_dependents();
+  pdl_wait();                                                   // queries and this step's keys/values come from earlier kernels
+  for (int idx = tid; idx < 16 * CHUNKS; idx += THREADS) {
+    const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
+    const bool ok = row < M;
+    const int tok = ok ? row / G : 0, hd = ok ? hk * G + (row - tok * G) : 0;
+    cp_async16(Qs + row * LDS + ch * 8, p.qkv + (size_t)(q0 + tok) * p.q_stride + (size_t)hd * D + ch * 8, ok);
+  }
+  cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();                                              // queries and table entries are in shared memory
 
@@ -741,7 +752,7 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   }
   if (which & 2) {
     if (p.G > 16) return SB_ERR_SHAPE;   // the caller sends such groups to the wide shape
-    if (num_splits < 1 || split_size <= 0 || (split_size % BN)) return SB_ERR_SHAPE;
+    if (num_splits < 1 || num_splits > 65535) return SB_ERR_SHAPE;
     if (num_splits > 1) {
       if (!scratch) return SB_ERR_SHAPE;
       p.part_o = (float*)scratch;
@@ -752,13 +763,11 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
     // bit 2 of ``which``: some request has more than 8 rows (the caller knows the largest token count)
     auto k_lower = attention_deep_kernel<false>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k_lower, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k_lower<<<dim3(num_splits, Hkv, n_rows), THREADS, smem, stream>>>(p);
-    SB_LAUNCH_CHECK();
+    SB_PDL_CHECK(launch_pdl(k_lower, dim3(num_splits, Hkv, n_rows), dim3(THREADS), smem, stream, p));
     if (which & 4) {
       auto k_upper = attention_deep_kernel<true>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(k_upper, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      k_upper<<<dim3(num_splits, Hkv, n_rows), THREADS, smem, stream>>>(p);
-      SB_LAUNCH_CHECK();
+      SB_PDL_CHECK(launch_pdl(k_upper, dim3(num_splits, Hkv, n_rows), dim3(THREADS), smem, stream, p));
     }
     if (num_splits > 1 && tickets == nullptr) {
       attention_merge_kernel<<<dim3(Hkv, n_rows), THREADS, 0, stream>>>(p);

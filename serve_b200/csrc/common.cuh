@@ -27,7 +27,44 @@
     if (e_ != cudaSuccess) return (int)e_;     \
   } while (0)
 
+#include <stdlib.h>
+
 namespace sb {
+
+// Programmatic dependent launch: a kernel launched through launch_pdl may start while its predecessor in the
+// stream is still running. It must call pdl_wait() before it reads anything an earlier kernel wrote, and before
+// it writes anything an earlier kernel may still read; what it does before that (fetching weights and tables the
+// step does not change, computing addresses) overlaps with the predecessor's tail. pdl_launch_dependents() lets
+// the successor be scheduled as early as possible. Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static const bool on = (getenv("SERVE_B200_NO_PDL") == nullptr);
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define SB_PDL_CHECK(expr)                        \
+  do {                                            \
+    cudaError_t e_ = (expr);                      \
+    if (e_ != cudaSuccess) return (int)e_;        \
+  } while (0)
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

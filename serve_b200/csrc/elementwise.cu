@@ -13,6 +13,8 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out,
                                  int dim, int vocab) {
   const int t = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   int tok = tokens[t];
   const bool ok = tok >= 0 && tok < vocab;
   const T* src = table + (size_t)(ok ? tok : 0) * dim;
@@ -26,12 +28,12 @@ SB_EXPORT int sb_embedding(const int* tokens, const void* table, float* out, int
   if (dim <= 0 || vocab <= 0) return SB_ERR_SHAPE;
   const int threads = dim >= 1024 ? 256 : 128;
   if (dtype == SB_DTYPE_F32)
-    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, dim, vocab);
+    SB_PDL_CHECK(launch_pdl(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, dim, vocab));
   else if (dtype == SB_DTYPE_BF16)
-    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, dim, vocab);
+    SB_PDL_CHECK(launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
+                            (const __nv_bfloat16*)table, out, dim, vocab));
   else
     return SB_ERR_DTYPE;
-  SB_LAUNCH_CHECK();
   return 0;
 }
 
@@ -102,9 +104,15 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restric
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) wv[k] = Vec4<W>::load(weight + i * 4);    // not written by any kernel of the step
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
     if (i < nvec) {
       v[k] = Vec4<float>::load(xr + i * 4);
-      wv[k] = Vec4<W>::load(weight + i * 4);
       if (dr) {
         const float4 d = Vec4<T>::load(dr + i * 4);
         v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
@@ -151,7 +159,6 @@ static int launch_add_rmsnorm(float* x, const void* delta, const int* rows, cons
         return SB_ERR_DTYPE;
       }
 #undef SB_NORM_VEC
-      SB_LAUNCH_CHECK();
       return 0;
     }
   }
@@ -250,10 +257,12 @@ __global__ void __launch_bounds__(ROPE_THREADS) rope_cache_write_kernel(
     const int i0 = pairing == 0 ? j : 2 * j;
     const int i1 = pairing == 0 ? j + half : 2 * j + 1;
     T* hv = row + (size_t)h * D;
-    const float a = to_float(hv[i0]), b = to_float(hv[i1]);
     const float ang = (float)pos * inv_freq[j];
     float sn, cs;
     sincosf(ang, &sn, &cs);
+    pdl_launch_dependents();
+    pdl_wait();                      // positions, tables and angles came before; q and k come from the kernel before
+    const float a = to_float(hv[i0]), b = to_float(hv[i1]);
     const T o0 = from_float<T>(a * cs - b * sn);
     const T o1 = from_float<T>(b * cs + a * sn);
     if (h < H) {
@@ -266,6 +275,8 @@ __global__ void __launch_bounds__(ROPE_THREADS) rope_cache_write_kernel(
     }
     return;
   }
+  pdl_launch_dependents();
+  pdl_wait();
   if (!cache_ok) return;
   // copy blocks: all value elements, then key elements beyond the rotary width
   const int tail = D - rot;
@@ -301,16 +312,15 @@ SB_EXPORT int sb_rope_cache_write(void* qkv, const int* positions, const int* to
   if (rot_blocks + copy_blocks > 65535) return SB_ERR_LIMIT;
   dim3 grid(n_tokens, rot_blocks + copy_blocks);
   if (dtype == SB_DTYPE_F32)
-    rope_cache_write_kernel<float><<<grid, ROPE_THREADS, 0, stream>>>((float*)qkv, positions, token_row, inv_freq, pairing, rot, H,
-                                                                      Hkv, D, (float*)kc, (float*)vc, block_table, bt_width, ps,
-                                                                      num_pages, write_cache, rot_blocks, errors);
+    SB_PDL_CHECK(launch_pdl(rope_cache_write_kernel<float>, grid, dim3(ROPE_THREADS), 0, stream, (float*)qkv, positions, token_row,
+                            inv_freq, pairing, rot, H, Hkv, D, (float*)kc, (float*)vc, block_table, bt_width, ps, num_pages,
+                            write_cache, rot_blocks, errors));
   else if (dtype == SB_DTYPE_BF16)
-    rope_cache_write_kernel<__nv_bfloat16><<<grid, ROPE_THREADS, 0, stream>>>(
-        (__nv_bfloat16*)qkv, positions, token_row, inv_freq, pairing, rot, H, Hkv, D, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc,
-        block_table, bt_width, ps, num_pages, write_cache, rot_blocks, errors);
+    SB_PDL_CHECK(launch_pdl(rope_cache_write_kernel<__nv_bfloat16>, grid, dim3(ROPE_THREADS), 0, stream, (__nv_bfloat16*)qkv,
+                            positions, token_row, inv_freq, pairing, rot, H, Hkv, D, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc,
+                            block_table, bt_width, ps, num_pages, write_cache, rot_blocks, errors));
   else
     return SB_ERR_DTYPE;
-  SB_LAUNCH_CHECK();
   return 0;
 }
 
@@ -342,6 +352,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
   __shared__ int sidx[32];
   const int r = blockIdx.x;
   const float* lr = logits + (size_t)r * vocab;
+  pdl_launch_dependents();
+  pdl_wait();
   const float temp = temperature[r];
   const uint32_t req = (uint32_t)req_ids[r], tok = (uint32_t)tok_index[r];
   float best = -INFINITY;
@@ -383,8 +395,7 @@ SB_EXPORT int sb_sample(const float* logits, const float* temperature, const int
   if (n_rows <= 0) return 0;
   if (vocab <= 0) return SB_ERR_SHAPE;
   const int threads = vocab >= 4096 ? 1024 : 256;
-  sample_kernel<<<n_rows, threads, 0, stream>>>(logits, temperature, req_ids, tok_index, (uint32_t)(seed & 0xffffffffULL),
-                                                (uint32_t)(seed >> 32), vocab, out);
-  SB_LAUNCH_CHECK();
+  SB_PDL_CHECK(launch_pdl(sample_kernel, dim3(n_rows), dim3(threads), 0, stream, logits, temperature, req_ids, tok_index,
+                          (uint32_t)(seed & 0xffffffffULL), (uint32_t)(seed >> 32), vocab, out));
   return 0;
 }

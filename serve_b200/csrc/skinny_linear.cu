@@ -20,7 +20,6 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int BN = 8;       // output columns per block
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 v;
@@ -38,13 +37,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // MT: tiles of 16 activation rows (M <= 16*MT); HALF: only rows 0..7 of the single tile exist (M <= 8).
+// NT: tiles of 8 output columns per block (2 for very wide outputs: fewer, fatter blocks).
 // GU: fused gate/up with SwiGLU epilogue. OutT: bf16 or float.
-template <int MT, bool HALF, bool GU, typename OutT>
+template <int MT, bool HALF, int NT, bool GU, typename OutT>
 __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w,
                                                                 OutT* __restrict__ out, int M, int N, int K) {
   constexpr int NW = GU ? 2 : 1;
-  constexpr int UNROLL = (MT * NW > 1) ? 4 : 8;   // groups of 32 k-values whose loads are issued together
-  __shared__ float red[WARPS][NW][MT][16 * BN];
+  constexpr int NB = NW * NT;                        // 8-column tiles of w rows a lane streams
+  constexpr int BN = 8 * NT;                         // output columns per block
+  constexpr int UNROLL = (MT * NB > 1) ? 4 : 8;      // groups of 32 k-values whose loads are issued together
+  __shared__ float red[WARPS][NB][MT][16 * 8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, tq = lane & 3;
   const int n0 = blockIdx.x * BN;
@@ -53,10 +55,13 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
   const int per = (groups + WARPS - 1) / WARPS;
   const int g_lo = warp * per, g_hi = min(groups, g_lo + per);
 
-  const int rn = min(n0 + g, N - 1);   // clamped: columns beyond N are computed and dropped
-  const bf16* wp[NW];
-  wp[0] = w + (size_t)rn * K + tq * 8;
-  if (GU) wp[1] = w + (size_t)(N + rn) * K + tq * 8;
+  const bf16* wp[NB];   // tile u*NT + v: half u (gate/up), column tile v
+#pragma unroll
+  for (int v = 0; v < NT; ++v) {
+    const int rn = min(n0 + v * 8 + g, N - 1);   // clamped: columns beyond N are computed and dropped
+    wp[v] = w + (size_t)rn * K + tq * 8;
+    if (GU) wp[NT + v] = w + (size_t)(N + rn) * K + tq * 8;
+  }
   const bf16* xg[MT];
   const bf16* xh[MT];
   bool okg[MT], okh[MT];
@@ -68,21 +73,35 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
     xh[t] = a + (size_t)(okh[t] ? t * 16 + g + 8 : 0) * K + tq * 8;
   }
 
-  float c[NW][MT][4];
+  float c[NB][MT][4];
 #pragma unroll
-  for (int u = 0; u < NW; ++u)
+  for (int u = 0; u < NB; ++u)
 #pragma unroll
     for (int t = 0; t < MT; ++t) c[u][t][0] = c[u][t][1] = c[u][t][2] = c[u][t][3] = 0.f;
 
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 vw[UNROLL][NB];
+  // the weights do not depend on the kernel before this one: their first loads go out before the wait
+  if (g_lo < g_hi) {
+#pragma unroll
+    for (int j = 0; j < UNROLL; ++j) {
+      const size_t off = (size_t)(g_lo + j < g_hi ? g_lo + j : g_lo) * 32;
+#pragma unroll
+      for (int u = 0; u < NB; ++u) vw[j][u] = ld_stream(wp[u] + off);
+    }
+  }
+  pdl_launch_dependents();
+  pdl_wait();
   for (int gi = g_lo; gi < g_hi; gi += UNROLL) {
-    uint4 vw[UNROLL][NW], vg[UNROLL][MT], vh[UNROLL][MT];
+    uint4 vg[UNROLL][MT], vh[UNROLL][MT];
 #pragma unroll
     for (int j = 0; j < UNROLL; ++j) {
       const bool in = gi + j < g_hi;
       const size_t off = (size_t)(in ? gi + j : g_lo) * 32;
+      if (gi != g_lo) {
 #pragma unroll
-      for (int u = 0; u < NW; ++u) vw[j][u] = ld_stream(wp[u] + off);
+        for (int u = 0; u < NB; ++u) vw[j][u] = ld_stream(wp[u] + off);
+      }
 #pragma unroll
       for (int t = 0; t < MT; ++t) {
         vg[j][t] = ld_cached(xg[t] + off);       // always a valid address; masked below
@@ -101,7 +120,7 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
 #pragma unroll
     for (int j = 0; j < UNROLL; ++j) {
 #pragma unroll
-      for (int u = 0; u < NW; ++u) {
+      for (int u = 0; u < NB; ++u) {
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
           mma_bf16(c[u][t], vg[j][t].x, vh[j][t].x, vg[j][t].y, vh[j][t].y, vw[j][u].x, vw[j][u].y);
@@ -110,17 +129,17 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
       }
     }
   }
-  // partial sums of the 8 warps -> shared memory; element (m_local, n_local) at m_local*BN + n_local
+  // partial sums of the 8 warps -> shared memory; element (m_local, n_local) of a tile at m_local*8 + n_local
 #pragma unroll
-  for (int u = 0; u < NW; ++u)
+  for (int u = 0; u < NB; ++u)
 #pragma unroll
     for (int t = 0; t < MT; ++t) {
       float* r = red[warp][u][t];
-      r[g * BN + tq * 2] = c[u][t][0];
-      r[g * BN + tq * 2 + 1] = c[u][t][1];
+      r[g * 8 + tq * 2] = c[u][t][0];
+      r[g * 8 + tq * 2 + 1] = c[u][t][1];
       if (!HALF) {
-        r[(g + 8) * BN + tq * 2] = c[u][t][2];
-        r[(g + 8) * BN + tq * 2 + 1] = c[u][t][3];
+        r[(g + 8) * 8 + tq * 2] = c[u][t][2];
+        r[(g + 8) * 8 + tq * 2 + 1] = c[u][t][3];
       }
     }
   __syncthreads();
@@ -129,11 +148,12 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
     const int n = n0 + nl;
     if (m >= M || n >= N) continue;
     const int t = m >> 4, ml = m & 15;
+    const int vt = nl >> 3, nn = nl & 7;
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int wv = 0; wv < WARPS; ++wv) {
-      s0 += red[wv][0][t][ml * BN + nl];
-      if (GU) s1 += red[wv][NW - 1][t][ml * BN + nl];
+      s0 += red[wv][vt][t][ml * 8 + nn];
+      if (GU) s1 += red[wv][NB - NT + vt][t][ml * 8 + nn];
     }
     float v = s0;
     if (GU) {
@@ -145,18 +165,23 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
   }
 }
 
-template <int MT, bool HALF, bool GU, typename OutT>
+template <int MT, bool HALF, int NT, bool GU, typename OutT>
 int launch(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
-  skinny_linear_kernel<MT, HALF, GU, OutT><<<(N + BN - 1) / BN, THREADS, 0, stream>>>((const bf16*)a, (const bf16*)w, (OutT*)out, M, N, K);
-  SB_LAUNCH_CHECK();
+  SB_PDL_CHECK(launch_pdl(skinny_linear_kernel<MT, HALF, NT, GU, OutT>, dim3((N + 8 * NT - 1) / (8 * NT)), dim3(THREADS), 0, stream,
+                          (const bf16*)a, (const bf16*)w, (OutT*)out, M, N, K));
   return 0;
 }
 
 template <bool GU, typename OutT>
 int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
-  if (M <= 8) return launch<1, true, GU, OutT>(a, w, out, M, N, K, stream);
-  if (M <= 16 || GU) return launch<1, false, GU, OutT>(a, w, out, M, N, K, stream);
-  return launch<2, false, GU, OutT>(a, w, out, M, N, K, stream);
+  // more than ~8 blocks of 8 columns per SM: halve the block count, double the bytes each keeps in flight
+  const bool wide = !GU && N >= 148 * 8 * 8;
+  if (M <= 8) {
+    if (wide) return launch<1, true, 2, GU, OutT>(a, w, out, M, N, K, stream);
+    return launch<1, true, 1, GU, OutT>(a, w, out, M, N, K, stream);
+  }
+  if (M <= 16 || GU) return launch<1, false, 1, GU, OutT>(a, w, out, M, N, K, stream);
+  return launch<2, false, 1, GU, OutT>(a, w, out, M, N, K, stream);
 }
 
 }  // namespace

@@ -190,14 +190,15 @@ class CudaKernels:
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
             _DT[qkv.dtype], _stream()), "attention")
 
-    # Blocks the deep shape aims at: a few per SM, so that key splits fill the 148 SMs at small batches.
-    TARGET_BLOCKS = 148 * 8
+    # Thread blocks of the deep shape that fit the GPU at once (2 per SM): the key range of every request is
+    # cut into so many splits that one wave of blocks covers the batch.
+    TARGET_BLOCKS = 148 * 2
 
-    def split_plan(self, rows: int, kv_heads: int, max_kv: int):
-        """(split_size, num_splits) of the deep shape for a batch; a function of sizes only, never of data."""
-        want = max(1, self.TARGET_BLOCKS // max(1, rows * kv_heads))
-        split_size = max(256, -(-(-(-max_kv // want)) // 64) * 64)
-        return split_size, max(1, -(-max_kv // split_size))
+    def split_plan(self, rows: int, kv_heads: int, max_kv: int) -> int:
+        """Number of key splits of the deep shape for a batch; a function of sizes only, never of data.
+        (Each request's own length is then shared out evenly over the splits inside the kernel.)"""
+        want = max(1, round(self.TARGET_BLOCKS / max(1, rows * kv_heads)))
+        return max(1, min(want, -(-max_kv // 128)))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
                        scale, window, out, shape) -> None:
@@ -212,7 +213,7 @@ class CudaKernels:
                 which |= 4      # some request of the deep shape may have more than 8 rows
         split_size, num_splits, scratch, tickets = 64, 1, None, None
         if which & 2:
-            split_size, num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
+            num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
             if num_splits > 1:
                 nbytes = lib.sb_attention_mma_scratch_bytes(shape.rows, kv_heads, num_splits)
                 scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
