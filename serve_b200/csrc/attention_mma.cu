@@ -75,31 +75,64 @@ struct Params {
   int* tickets;     // [R, Hkv] zero before the launch and again after it; nullptr: a separate kernel merges
 };
 
+constexpr int MAX_SPLITS = 32;
+
 // Partial results of all key splits of (request r, kv head hk) -> the output rows. Reads bypass L1: the
-// partials were written by other SMs.
-__device__ __forceinline__ void merge_splits(const Params& p, int r, int hk, int q0, int M) {
+// partials were written by other SMs. First the (max, sum) pairs of all splits are fetched at once and turned
+// into one factor per (split, row); then every output element adds its S scaled partials, loads unrolled.
+// ``work``: (MAX_SPLITS + 1) * 16 floats of shared memory nobody else uses any more.
+__device__ __forceinline__ void merge_splits(const Params& p, int r, int hk, int q0, int M, int nthreads, float* work) {
+  float (*f_s)[16] = reinterpret_cast<float (*)[16]>(work);
+  float* inv_s = work + MAX_SPLITS * 16;
   const int S = p.num_splits;
   const size_t base = ((size_t)r * p.Hkv + hk) * S;
-  for (int idx = threadIdx.x; idx < M * D; idx += THREADS) {
-    const int row = idx / D, d = idx - row * D;
+  for (int idx = threadIdx.x; idx < S * 16; idx += nthreads) {
+    const int s_ = idx >> 4, row = idx & 15;
+    f_s[s_][row] = row < M ? __ldcg(p.part_ml + ((base + s_) * 16 + row) * 2) : -INFINITY;
+  }
+  __syncthreads();
+  if (threadIdx.x < 16) {
+    const int row = threadIdx.x;
     float mm = -INFINITY;
-    for (int s = 0; s < S; ++s) mm = fmaxf(mm, __ldcg(p.part_ml + ((base + s) * 16 + row) * 2));
-    float ll = 0.f, acc = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float ms = __ldcg(p.part_ml + ((base + s) * 16 + row) * 2);
-      if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - mm);
-      ll += __ldcg(p.part_ml + ((base + s) * 16 + row) * 2 + 1) * f;
-      acc += __ldcg(p.part_o + ((base + s) * 16 + row) * D + d) * f;
+    for (int s_ = 0; s_ < S; ++s_) mm = fmaxf(mm, f_s[s_][row]);
+    float ll = 0.f;
+    for (int s_ = 0; s_ < S; ++s_) {
+      const float ms = f_s[s_][row];
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+      if (f != 0.f) ll += __ldcg(p.part_ml + ((base + s_) * 16 + row) * 2 + 1) * f;
+      f_s[s_][row] = f;
+    }
+    inv_s[row] = ll > 0.f ? 1.f / ll : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < M * D; idx += nthreads) {
+    const int row = idx / D, d = idx - row * D;
+    float acc = 0.f;
+    int s_ = 0;
+    for (; s_ + 4 <= S; s_ += 4) {
+      const float v0 = __ldcg(p.part_o + ((base + s_) * 16 + row) * D + d);
+      const float v1 = __ldcg(p.part_o + ((base + s_ + 1) * 16 + row) * D + d);
+      const float v2 = __ldcg(p.part_o + ((base + s_ + 2) * 16 + row) * D + d);
+      const float v3 = __ldcg(p.part_o + ((base + s_ + 3) * 16 + row) * D + d);
+      // a split without keys wrote no partial output: its factor is 0 and its (stale) values are not touched
+      const float f0 = f_s[s_][row], f1 = f_s[s_ + 1][row], f2 = f_s[s_ + 2][row], f3 = f_s[s_ + 3][row];
+      acc = f0 != 0.f ? fmaf(v0, f0, acc) : acc;
+      acc = f1 != 0.f ? fmaf(v1, f1, acc) : acc;
+      acc = f2 != 0.f ? fmaf(v2, f2, acc) : acc;
+      acc = f3 != 0.f ? fmaf(v3, f3, acc) : acc;
+    }
+    for (; s_ < S; ++s_) {
+      const float f = f_s[s_][row];
+      if (f != 0.f) acc = fmaf(__ldcg(p.part_o + ((base + s_) * 16 + row) * D + d), f, acc);
     }
     const int tok = row / p.G, hd = hk * p.G + (row - tok * p.G);
-    p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(acc * inv_s[row]);
   }
 }
 
 // Called by every block of a split launch once its partial results are written: the block that arrives last
 // merges. Nobody waits for anybody.
-__device__ __forceinline__ void finish_split(const Params& p, int r, int hk, int q0, int M) {
+__device__ __forceinline__ void finish_split(const Params& p, int r, int hk, int q0, int M, int nthreads, float* work) {
   if (p.tickets == nullptr) return;
   __shared__ int s_last;
   __threadfence();
@@ -111,11 +144,11 @@ __device__ __forceinline__ void finish_split(const Params& p, int r, int hk, int
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  merge_splits(p, r, hk, q0, M);
+  merge_splits(p, r, hk, q0, M, nthreads, work);
   if (threadIdx.x == 0) p.tickets[(size_t)r * p.Hkv + hk] = 0;
 }
 
-constexpr int BT_CACHE = 512;        // block-table entries a thread block keeps in shared memory
+constexpr int BT_CACHE = 256;        // block-table entries a thread block keeps in shared memory
 
 // Fetch keys [kt, kt+BN) of kv head hk into one stage of shared memory; keys outside [lo, hi) become zeros.
 // bt points at the table entry of block bt_first (shared memory copy, or the table itself with bt_first 0).
@@ -190,7 +223,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
       float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
       ml[0] = -INFINITY; ml[1] = 0.f;
     }
-    if (p.num_splits > 1) finish_split(p, r, hk, q0, M);
+    if (p.num_splits > 1) finish_split(p, r, hk, q0, M, THREADS, reinterpret_cast<float*>(smem_raw));
     return;
   }
 
@@ -383,7 +416,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
         if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
       }
     }
-    if (!last) finish_split(p, r, hk, q0, M);
+    if (!last) finish_split(p, r, hk, q0, M, THREADS, reinterpret_cast<float*>(smem_raw));
   }
 }
 
@@ -443,12 +476,14 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
   }
 }
 
-template <bool UPPER>
-__global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p) {
+// NWARPS: 4 when many blocks share an SM, 8 when a block has an SM to itself (small batches).
+template <bool UPPER, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Params p) {
+  constexpr int NTHR = NWARPS * 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int bt_s[BT_CACHE];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][LDS]
-  bf16* KVs = Qs + 16 * LDS;                                    // [4 warps][DSTAGES][K DKWxLDS, V DKWxLDS]
+  bf16* KVs = Qs + 16 * LDS;                                    // [NWARPS][DSTAGES][K DKWxLDS, V DKWxLDS]
 
   const int r = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
@@ -462,7 +497,7 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
   int hi = p0 + (M - 1) / G + 1;
   {
     // the request's keys are shared out evenly over the launch's splits, in units of one step of all four warps
-    constexpr int UNIT = 4 * DKW;
+    constexpr int UNIT = NWARPS * DKW;
     const int split_size = max(UNIT, ((hi - lo + p.num_splits - 1) / p.num_splits + UNIT - 1) / UNIT * UNIT);
     const int base = (lo / UNIT) * UNIT;
     lo = max(lo, base + split * split_size);
@@ -480,21 +515,21 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
       float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
       ml[0] = -INFINITY; ml[1] = 0.f;
     }
-    if (p.num_splits > 1) finish_split(p, r, hk, q0, M);
+    if (p.num_splits > 1) finish_split(p, r, hk, q0, M, NTHR, reinterpret_cast<float*>(smem_raw));
     return;
   }
   {
     // lengths and block tables are the step's own inputs: fetched while the kernel before this one finishes
     const int b_lo = lo / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
     if (b_hi - b_lo + 1 <= BT_CACHE) {
-      for (int i = tid; i <= b_hi - b_lo; i += THREADS) bt_s[i] = bt[b_lo + i];
+      for (int i = tid; i <= b_hi - b_lo; i += NTHR) bt_s[i] = bt[b_lo + i];
       bt = bt_s;
       bt_first = b_lo;
     }
   }
   pdl_launch_dependents();
   pdl_wait();                                                   // queries and this step's keys/values come from earlier kernels
-  for (int idx = tid; idx < 16 * CHUNKS; idx += THREADS) {
+  for (int idx = tid; idx < 16 * CHUNKS; idx += NTHR) {
     const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
     const bool ok = row < M;
     const int tok = ok ? row / G : 0, hd = ok ? hk * G + (row - tok * G) : 0;
@@ -507,11 +542,11 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
   const bool same_page = (p.ps % DKW) == 0;
   const int k_first = (lo / DKW) * DKW;
   const int n_sub = (hi - k_first + DKW - 1) / DKW;             // sub-tiles of the split
-  const int my_n = (n_sub - warp + 3) / 4;                      // this warp's share: sub-tiles warp, warp+4, ...
+  const int my_n = (n_sub - warp + NWARPS - 1) / NWARPS;        // this warp's share: sub-tiles warp, warp+NWARPS, ...
   bf16* myKV = KVs + (size_t)warp * DSTAGES * 2 * DKW * LDS;
 #pragma unroll
   for (int s = 0; s < DSTAGES - 1; ++s) {
-    if (s < my_n) load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + 4 * s) * DKW, lo, hi, same_page, myKV + s * 2 * DKW * LDS,
+    if (s < my_n) load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + NWARPS * s) * DKW, lo, hi, same_page, myKV + s * 2 * DKW * LDS,
                                   myKV + s * 2 * DKW * LDS + DKW * LDS, lane);
     cp_async_commit();
   }
@@ -536,7 +571,7 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
       const int nx = it + DSTAGES - 1;
       if (nx < my_n) {
         bf16* Kn = myKV + (nx % DSTAGES) * 2 * DKW * LDS;
-        load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + 4 * nx) * DKW, lo, hi, same_page, Kn, Kn + DKW * LDS, lane);
+        load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + NWARPS * nx) * DKW, lo, hi, same_page, Kn, Kn + DKW * LDS, lane);
       }
       cp_async_commit();
       cp_async_wait<DSTAGES - 1>();
@@ -544,7 +579,7 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
     __syncwarp();
     const bf16* Ks = myKV + (it % DSTAGES) * 2 * DKW * LDS;
     const bf16* Vs = Ks + DKW * LDS;
-    const int kbase = k_first + (warp + 4 * it) * DKW;
+    const int kbase = k_first + (warp + NWARPS * it) * DKW;
     float s[DNT][4];
 #pragma unroll
     for (int j = 0; j < DNT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -653,8 +688,8 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
   __syncthreads();                                              // every warp is done with its stages: reuse the memory
-  float* Om = reinterpret_cast<float*>(smem_raw);               // [4][16][D]
-  float* MLm = Om + 4 * 16 * D;                                 // [4][16][2]
+  float* Om = reinterpret_cast<float*>(smem_raw);               // [NWARPS][16][D]
+  float* MLm = Om + NWARPS * 16 * D;                            // [NWARPS][16][2]
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) {
     float* d0 = Om + ((size_t)warp * 16 + g) * D + i * 8 + tq * 2;
@@ -668,14 +703,14 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
   }
   __syncthreads();
   const bool last = p.num_splits == 1;
-  for (int idx = tid; idx < M * D; idx += THREADS) {
+  for (int idx = tid; idx < M * D; idx += NTHR) {
     const int row = idx / D, d = idx - row * D;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, MLm[(w * 16 + row) * 2]);
+    for (int w = 0; w < NWARPS; ++w) mm = fmaxf(mm, MLm[(w * 16 + row) * 2]);
     float ll = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < NWARPS; ++w) {
       const float mw = MLm[(w * 16 + row) * 2];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
       ll += MLm[(w * 16 + row) * 2 + 1] * f;
@@ -690,13 +725,22 @@ __global__ void __launch_bounds__(THREADS) attention_deep_kernel(const Params p)
       if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
     }
   }
-  if (!last) finish_split(p, r, hk, q0, M);
+  if (!last) finish_split(p, r, hk, q0, M, NTHR, reinterpret_cast<float*>(smem_raw));
 }
 
-size_t deep_smem_bytes() {
-  const size_t tiles = (size_t)(16 + 4 * DSTAGES * 2 * DKW) * LDS * sizeof(bf16);
-  const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+size_t deep_smem_bytes(int nwarps) {
+  const size_t tiles = (size_t)(16 + nwarps * DSTAGES * 2 * DKW) * LDS * sizeof(bf16);
+  const size_t merge = (size_t)(nwarps * 16 * D + nwarps * 16 * 2) * sizeof(float);
   return tiles > merge ? tiles : merge;
+}
+
+template <bool UPPER, int NWARPS>
+int launch_deep(const Params& p, int n_rows, cudaStream_t stream) {
+  auto k = attention_deep_kernel<UPPER, NWARPS>;
+  const size_t smem = deep_smem_bytes(NWARPS);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  SB_PDL_CHECK(launch_pdl(k, dim3(p.num_splits, p.Hkv, n_rows), dim3(NWARPS * 32), smem, stream, p));
+  return 0;
 }
 
 // Merge the partial results of the key splits of the deep shape. grid (Hkv, R), 128 threads.
@@ -705,7 +749,8 @@ __global__ void __launch_bounds__(THREADS) attention_merge_kernel(const Params p
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int M = qn * p.G;
   if (M > 16 || M <= 0) return;
-  merge_splits(p, r, hk, q0, M);
+  __shared__ float work[(MAX_SPLITS + 1) * 16];
+  merge_splits(p, r, hk, q0, M, THREADS, work);
 }
 
 template <int WM, int WN> size_t smem_bytes() {
@@ -752,22 +797,21 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   }
   if (which & 2) {
     if (p.G > 16) return SB_ERR_SHAPE;   // the caller sends such groups to the wide shape
-    if (num_splits < 1 || num_splits > 65535) return SB_ERR_SHAPE;
+    if (num_splits < 1 || num_splits > MAX_SPLITS) return SB_ERR_SHAPE;
     if (num_splits > 1) {
       if (!scratch) return SB_ERR_SHAPE;
       p.part_o = (float*)scratch;
       p.part_ml = p.part_o + (size_t)n_rows * Hkv * num_splits * 16 * D;
       p.tickets = tickets;
     }
-    const size_t smem = deep_smem_bytes();
-    // bit 2 of ``which``: some request has more than 8 rows (the caller knows the largest token count)
-    auto k_lower = attention_deep_kernel<false>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k_lower, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    SB_PDL_CHECK(launch_pdl(k_lower, dim3(num_splits, Hkv, n_rows), dim3(THREADS), smem, stream, p));
+    // bit 2 of ``which``: some request has more than 8 rows (the caller knows the largest token count).
+    // Few blocks (at most one per SM): 8 warps each, so that an SM still has warps to switch between.
+    const bool roomy = (long long)n_rows * Hkv * num_splits <= 148 && deep_smem_bytes(8) <= 227 * 1024;
+    int rc = roomy ? launch_deep<false, 8>(p, n_rows, stream) : launch_deep<false, 4>(p, n_rows, stream);
+    if (rc) return rc;
     if (which & 4) {
-      auto k_upper = attention_deep_kernel<true>;
-      if (smem > 48 * 1024) cudaFuncSetAttribute(k_upper, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      SB_PDL_CHECK(launch_pdl(k_upper, dim3(num_splits, Hkv, n_rows), dim3(THREADS), smem, stream, p));
+      rc = roomy ? launch_deep<true, 8>(p, n_rows, stream) : launch_deep<true, 4>(p, n_rows, stream);
+      if (rc) return rc;
     }
     if (num_splits > 1 && tickets == nullptr) {
       attention_merge_kernel<<<dim3(Hkv, n_rows), THREADS, 0, stream>>>(p);

@@ -192,13 +192,14 @@ class CudaKernels:
 
     # Thread blocks of the deep shape that fit the GPU at once (2 per SM): the key range of every request is
     # cut into so many splits that one wave of blocks covers the batch.
-    TARGET_BLOCKS = 148 * 2
+    TARGET_BLOCKS = 148
+    MAX_SPLITS = 32
 
     def split_plan(self, rows: int, kv_heads: int, max_kv: int) -> int:
         """Number of key splits of the deep shape for a batch; a function of sizes only, never of data.
         (Each request's own length is then shared out evenly over the splits inside the kernel.)"""
-        want = max(1, round(self.TARGET_BLOCKS / max(1, rows * kv_heads)))
-        return max(1, min(want, -(-max_kv // 128)))
+        want = max(1, self.TARGET_BLOCKS // max(1, rows * kv_heads))
+        return max(1, min(want, -(-max_kv // 256), self.MAX_SPLITS))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
                        scale, window, out, shape) -> None:
