@@ -820,3 +820,69 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Decoding attention with built-in scratch memory, for callers that must not allocate (attention_noalloc.h).
+#include "attention_noalloc.h"
+
+namespace {
+constexpr size_t kNoallocPartialFloats = (size_t)SB_NOALLOC_MAX_TILES * 16 * (D + 2);
+// partial outputs and (max, sum) pairs of the key splits, then one arrival counter per (request, kv head)
+static __device__ __align__(256) float g_noalloc_scratch[kNoallocPartialFloats + SB_NOALLOC_MAX_TILES];
+// In host code the name above is only a handle; the device address is looked up once per device.
+constexpr int kNoallocMaxDevices = 64;
+void* g_noalloc_addr[kNoallocMaxDevices];
+}  // namespace
+
+SB_EXPORT int sb_attention_decode_noalloc_max_tiles(void) { return SB_NOALLOC_MAX_TILES; }
+
+SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
+                                          int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages,
+                                          float scale, int window, void* out, int n_rows, int max_q, int num_splits,
+                                          cudaStream_t stream) {
+  if (n_rows <= 0 || max_q <= 0) return 0;
+  if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
+  const int G = H / Hkv;
+  if (G > 16 || (long long)max_q * G > 16) return SB_ERR_SHAPE;
+  if (num_splits < 1 || num_splits > MAX_SPLITS) return SB_ERR_SHAPE;
+  if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
+  if ((long long)n_rows * Hkv * num_splits > SB_NOALLOC_MAX_TILES) return SB_ERR_LIMIT;
+  if ((q_stride % 8) || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || !aligned16(out)) return SB_ERR_ALIGN;
+
+  // set-up, once per device, with that device current: the array's address on this device
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoallocMaxDevices) return SB_ERR_LIMIT;
+  if (g_noalloc_addr[dev] == nullptr) {
+    void* addr = nullptr;
+    e = cudaGetSymbolAddress(&addr, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_addr[dev] = addr;
+  }
+  float* scratch = static_cast<float*>(g_noalloc_addr[dev]);
+  int* tickets = reinterpret_cast<int*>(scratch + kNoallocPartialFloats);
+
+  Params p;
+  p.qkv = (const bf16*)qkv; p.q_stride = q_stride; p.kc = (const bf16*)kc; p.vc = (const bf16*)vc;
+  p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
+  p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
+  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
+  p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+  if (num_splits > 1) {
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)n_rows * Hkv * num_splits * 16 * D;
+    p.tickets = tickets;
+    // the array keeps the last call's contents; the arrival counters are what has to start at zero
+    e = cudaMemsetAsync(tickets, 0, (size_t)n_rows * Hkv * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const bool roomy = (long long)n_rows * Hkv * num_splits <= 148 && deep_smem_bytes(8) <= 227 * 1024;
+  int rc = roomy ? launch_deep<false, 8>(p, n_rows, stream) : launch_deep<false, 4>(p, n_rows, stream);
+  if (rc) return rc;
+  if ((long long)max_q * G > 8 || G > 8) {
+    rc = roomy ? launch_deep<true, 8>(p, n_rows, stream) : launch_deep<true, 4>(p, n_rows, stream);
+    if (rc) return rc;
+  }
+  return 0;
+}
