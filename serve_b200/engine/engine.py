@@ -104,11 +104,6 @@ class Engine:
         """Run one batch (see Stepper.step); float32 logits [wanted, vocab] or None.
 
         The returned tensor may be overwritten by the next step: use or copy it first."""
-        vocab = self.spec.vocab_size
-        for e in entries:
-            for tok in e.tokens:
-                if not (0 <= int(tok) < vocab):
-                    raise ValueError(f"request {e.rid!r}: token id {tok} is outside the vocabulary of {vocab}")
         return self.stepper.step(entries)
 
     def end(self, rid: Hashable) -> None:

@@ -143,6 +143,12 @@ class Stepper:
             raise
         return batch
 
+    def _undo_plan(self, batch) -> None:
+        """A step that is refused after its pages were reserved gives back requests it had just opened."""
+        for rid, _n in batch:
+            if self.cache.is_open(rid) and self.cache.length(rid) == 0:
+                self.cache.close(rid)
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch; returns [wanted, vocab] float32 logits (None if nothing is wanted)."""
         batch = self.plan(entries)
@@ -169,21 +175,34 @@ class Stepper:
         kv_o, _ = lay.spans["kv_len"]
         sl_o, _ = lay.spans["slots"]
         lr_o, _ = lay.spans["logit_rows"]
-        at = 0
-        li = 0
-        h[cu_o] = 0
-        for i, e in enumerate(entries):
-            n = q_lens[i]
-            h[o + at: o + at + n] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
-            h[pos_o + at: pos_o + at + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
-            h[row_o + at: row_o + at + n] = i
-            for w in e.want:
-                h[lr_o + li] = at + w
-                li += 1
-            at += n
-            h[cu_o + i + 1] = at
-            h[kv_o + i] = new_lens[i]
-            h[sl_o + i] = self.cache.slot(e.rid)
+        # vectorised packing: a handful of numpy calls however many requests the step has
+        ql = np.asarray(q_lens, dtype=np.int64)
+        cu = np.zeros(r + 1, dtype=np.int64)
+        np.cumsum(ql, out=cu[1:])
+        if pure_decode:
+            toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=r)
+            row_of = np.arange(r, dtype=np.int64)
+            pos = np.asarray(starts, dtype=np.int64)
+        else:
+            toks = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+            row_of = np.repeat(np.arange(r, dtype=np.int64), ql)
+            pos = np.arange(t, dtype=np.int64) - cu[:-1][row_of] + np.asarray(starts, dtype=np.int64)[row_of]
+        vocab = self.model.spec.vocab_size
+        if toks.min() < 0 or toks.max() >= vocab:
+            bad = int(toks[(toks < 0) | (toks >= vocab)][0])
+            self._undo_plan(batch)
+            raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
+        h[o: o + t] = toks
+        h[pos_o: pos_o + t] = pos
+        h[row_o: row_o + t] = row_of
+        h[cu_o: cu_o + r + 1] = cu
+        h[kv_o: kv_o + r] = new_lens
+        h[sl_o: sl_o + r] = [self.cache.slot(rid) for rid in rids]
+        if n_want:
+            if pure_decode and n_want == r:
+                h[lr_o: lr_o + r] = np.arange(r)
+            else:
+                h[lr_o: lr_o + n_want] = [int(cu[i]) + w for i, e in enumerate(entries) for w in e.want]
         for gi, (off, rr, w) in enumerate(lay.tables):
             rows = self.cache.table_rows(gi, rids, w)
             h[off: off + rr * w] = rows.reshape(-1)

@@ -21,6 +21,9 @@ class Sampler:
         self.device = torch.device(device)
         self.seed = int(seed) & 0xFFFFFFFFFFFFFFFF
         self._pin = self.device.type == "cuda"
+        self._host = None     # pinned staging [3, cap] int32: temperatures (as float bits), request ids, token indices
+        self._dev = None
+        self._event = None
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], request_ids: Sequence[int],
                token_indices: Sequence[int]) -> torch.Tensor:
@@ -30,9 +33,21 @@ class Sampler:
             raise ValueError("one temperature, request id and token index per row of logits is needed")
         if any(t < 0 for t in temperatures):
             raise ValueError("temperature must not be negative")
-        meta_f = torch.tensor(list(temperatures), dtype=torch.float32, pin_memory=self._pin).to(self.device, non_blocking=True)
-        meta_i = torch.tensor([list(request_ids), list(token_indices)], dtype=torch.int32, pin_memory=self._pin).to(
-            self.device, non_blocking=True)
+        if self._host is None or self._host.shape[1] < n:
+            cap = max(64, 1 << (n - 1).bit_length())
+            self._host = torch.empty((3, cap), dtype=torch.int32, pin_memory=self._pin)
+            self._dev = torch.empty((3, cap), dtype=torch.int32, device=self.device)
+        if self._event is not None:
+            self._event.synchronize()       # the copy that last used the staging buffer has finished
+        h = self._host.numpy()
+        h[0, :n].view("float32")[:] = temperatures
+        h[1, :n] = request_ids
+        h[2, :n] = token_indices
+        self._dev.copy_(self._host, non_blocking=True)
+        if self._pin:
+            if self._event is None:
+                self._event = torch.cuda.Event()
+            self._event.record()
         out = torch.empty(n, dtype=torch.int32, device=self.device)
-        self.kernels.sample(logits, meta_f, meta_i[0], meta_i[1], self.seed, out)
+        self.kernels.sample(logits, self._dev[0, :n].view(torch.float32), self._dev[1, :n], self._dev[2, :n], self.seed, out)
         return out
