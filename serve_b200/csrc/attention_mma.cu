@@ -5,9 +5,9 @@
 // row dimension, row m of a request's tile standing for (token m / G, head hk*G + m % G), so a key/value
 // tile is fetched once for the whole group. Two shapes of thread block exist:
 //   * "wide" (4 warps x 16 rows = 64 rows, every warp walks all keys of a 64-key tile): prompt portions;
-//   * "deep" (16 rows, the 4 warps split the keys of a tile, results merged through shared memory; the
-//     key range may also be split over several blocks whose partial results a second kernel merges):
-//     requests that bring at most 16 / G tokens, i.e. decoding.
+//   * "deep" (16 rows, the warps deal the keys out among themselves, each with a pipeline of its own, results
+//     merged through shared memory; the key range may also be split over several blocks whose partial
+//     results the block that finishes last merges): requests that bring at most 16 / G tokens, i.e. decoding.
 // A request is handled by the shape its row count fits; the other shape's blocks leave it alone.
 //
 // Scores, running maxima, sums and outputs are float; probabilities are rounded to bfloat16 for the
@@ -172,62 +172,46 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
 }
 
 // WM warps along rows, WN warps along the keys of a tile (WM * WN == 4).
-// Stages of the key/value pipeline: decoding blocks do little arithmetic per byte and want many loads in flight.
-__host__ __device__ constexpr int stages_for(bool deep) { return deep ? (D <= 64 ? 4 : (D <= 128 ? 3 : 2)) : 2; }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
-template <int WM, int WN>
-__global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) {
-  constexpr int BM = WM * 16;
-  constexpr int KW = BN / WN;          // keys per warp per tile
-  constexpr int NT = KW / 8;           // score n-tiles per warp
-  constexpr bool DEEP = (WN > 1);
-  constexpr int NSTAGE = stages_for(DEEP);
+// The wide shape: requests with more than 16 rows (prompt portions). grid (row tiles of 64, Hkv, R), 4 warps,
+// each warp 16 rows against all 64 keys of a tile; two stages of keys/values. Tiles wholly below every row's
+// position (and inside every row's window) skip the mask; the heaviest row tiles (the last ones) start first.
+constexpr bool WQ_IN_REGS = D <= 128;
+
+__global__ void __launch_bounds__(THREADS) attention_wide_kernel(const Params p) {
+  constexpr int BM = 64;
+  constexpr int NT = BN / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int bt_s[BT_CACHE];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [BM][LDS]
-  bf16* KVs = Qs + BM * LDS;                        // NSTAGE stages x (K [BN][LDS], V [BN][LDS])
+  bf16* KVs = Qs + BM * LDS;                        // 2 stages x (K [BN][LDS], V [BN][LDS])
 
   const int r = blockIdx.z, hk = blockIdx.y;
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int G = p.G;
   const int M = qn * G;                             // rows of this (request, kv head)
-  int m0, split;
-  if (DEEP) {
-    if (M > 16 || M <= 0) return;                   // the wide shape takes this request
-    m0 = 0; split = blockIdx.x;
-  } else {
-    if (M <= 16) return;                            // the deep shape takes this request
-    m0 = blockIdx.x * BM; split = 0;
-    if (m0 >= M) return;
-  }
+  if (M <= 16) return;                              // the deep shape takes this request
+  const int n_mtiles = (M + BM - 1) / BM;
+  if ((int)blockIdx.x >= n_mtiles) return;
+  const int m0 = (n_mtiles - 1 - (int)blockIdx.x) * BM;   // later rows see more keys: they go first
   const int L = p.kv_len[r];
   const int p0 = L - qn;                            // position of the request's first query
-  const int tok_first = m0 / G, tok_last = min(m0 + BM, M) - 1;
-  int lo = p.window > 0 ? max(0, p0 + tok_first - p.window + 1) : 0;
-  int hi = p0 + tok_last / G + 1;                   // exclusive, <= L
-  if (DEEP) {
-    // this block's share of the keys
-    const int s_lo = split * p.split_size, s_hi = s_lo + p.split_size;
-    lo = max(lo, s_lo);
-    hi = min(hi, s_hi);
-  }
+  const int tok_first = m0 / G, row_last = min(m0 + BM, M) - 1;
+  const int lo = p.window > 0 ? max(0, p0 + tok_first - p.window + 1) : 0;
+  const int hi = p0 + row_last / G + 1;             // exclusive, <= L
+  // keys every row of the tile may see without a mask
+  const int free_lo = p.window > 0 ? max(lo, p0 + row_last / G - p.window + 1) : lo;
+  const int free_hi = min(hi, p0 + tok_first + 1);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int wm = DEEP ? 0 : warp, wn = DEEP ? warp : 0;
   const int g = lane >> 2, tq = lane & 3;
   const int* bt = p.block_table + (size_t)r * p.bt_width;
   int bt_first = 0;
 
-  if (DEEP && lo >= hi) {
-    // no keys fall to this split: say so, so that the merge skips it
-    if (tid < 16) {
-      float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
-      ml[0] = -INFINITY; ml[1] = 0.f;
-    }
-    if (p.num_splits > 1) finish_split(p, r, hk, q0, M, THREADS, reinterpret_cast<float*>(smem_raw));
-    return;
-  }
-
-  // queries -> shared memory (rows beyond M are zeros)
   for (int idx = tid; idx < BM * CHUNKS; idx += THREADS) {
     const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
     const int m = m0 + row;
@@ -238,7 +222,6 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
   const int kt0 = (lo / BN) * BN;
   const int n_tiles = (hi - kt0 + BN - 1) / BN;
   {
-    // the table entries of this block's keys, once, instead of a dependent global load per row and tile
     const int b_lo = lo / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
     if (b_hi - b_lo + 1 <= BT_CACHE) {
       for (int i = tid; i <= b_hi - b_lo; i += THREADS) bt_s[i] = bt[b_lo + i];
@@ -247,16 +230,12 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
       bt_first = b_lo;
     }
   }
-#pragma unroll
-  for (int s = 0; s < NSTAGE - 1; ++s) {
-    if (s < n_tiles) load_kv_tile(p, bt, bt_first, hk, kt0 + s * BN, lo, hi, KVs + s * 2 * BN * LDS, KVs + s * 2 * BN * LDS + BN * LDS);
-    cp_async_commit();
-  }
+  load_kv_tile(p, bt, bt_first, hk, kt0, lo, hi, KVs, KVs + BN * LDS);
+  cp_async_commit();
 
-  // positions of this thread's two rows (g and g+8 of the warp's 16)
-  const int row_a = m0 + wm * 16 + g, row_b = row_a + 8;
+  const int row_a = m0 + warp * 16 + g, row_b = row_a + 8;
   const int pos_a = row_a < M ? p0 + row_a / G : -1, pos_b = row_b < M ? p0 + row_b / G : -1;
-
+  uint32_t qf[WQ_IN_REGS ? D / 16 : 1][4];
   float o[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -264,46 +243,56 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
 
   for (int it = 0; it < n_tiles; ++it) {
     const int kt = kt0 + it * BN;
-    bf16* Ks = KVs + (it % NSTAGE) * 2 * BN * LDS;
+    bf16* Ks = KVs + (it & 1) * 2 * BN * LDS;
     bf16* Vs = Ks + BN * LDS;
-    {
-      // fetch NSTAGE-1 tiles ahead, into the stage the previous iteration has finished with
-      const int nx = it + NSTAGE - 1;
-      if (nx < n_tiles) {
-        bf16* Kn = KVs + (nx % NSTAGE) * 2 * BN * LDS;
-        load_kv_tile(p, bt, bt_first, hk, kt0 + nx * BN, lo, hi, Kn, Kn + BN * LDS);
-      }
-      cp_async_commit();           // an empty group when nothing was fetched: the count below stays right
-      cp_async_wait<NSTAGE - 1>();  // tile ``it`` (and the queries) have landed
+    if (it + 1 < n_tiles) {
+      bf16* Kn = KVs + ((it + 1) & 1) * 2 * BN * LDS;
+      load_kv_tile(p, bt, bt_first, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
-
-    const int kbase = kt + wn * KW;                 // first key of this warp's share
-    const bool warp_has_keys = kbase < hi && kbase + KW > lo;
-    if (warp_has_keys) {
-      // S = Q K^T for 16 rows x KW keys
-      float s[NT][4];
+    if (WQ_IN_REGS && it == 0) {
 #pragma unroll
-      for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], Qs + (warp * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+    }
+    float s[NT][4];
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        uint32_t a0, a1, a2, a3;
-        ldmatrix_x4(a0, a1, a2, a3, Qs + (wm * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+    for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-        for (int j = 0; j < NT; j += 2) {
-          uint32_t b0, b1, b2, b3;   // (keys j*8.., d lo), (keys j*8.., d hi), (keys (j+1)*8.., d lo), (keys (j+1)*8.., d hi)
-          ldmatrix_x4(b0, b1, b2, b3, Ks + (wn * KW + j * 8 + (lane >> 4) * 8 + (lane & 7)) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
-          mma_bf16(s[j], a0, a1, a2, a3, b0, b1);
-          mma_bf16(s[j + 1], a0, a1, a2, a3, b2, b3);
-        }
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t a0, a1, a2, a3;
+      if (WQ_IN_REGS) {
+        a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3];
+      } else {
+        ldmatrix_x4(a0, a1, a2, a3, Qs + (warp * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
       }
-      // scale, mask, running maximum
-      float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < NT; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, Ks + (j * 8 + (lane >> 4) * 8 + (lane & 7)) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[j], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[j + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+    if (kt >= free_lo && kt + BN <= free_hi) {
+      // (rows beyond M hold zero queries; what they compute is finite and never stored)
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        s[j][0] *= p.scale_log2; s[j][1] *= p.scale_log2; s[j][2] *= p.scale_log2; s[j][3] *= p.scale_log2;
+        mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
+        mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
+      }
+    } else {
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int key = kbase + j * 8 + tq * 2 + e;
+          const int key = kt + j * 8 + tq * 2 + e;
           const bool in_range = key >= lo && key < hi;
           const bool ok_a = in_range && key <= pos_a && (p.window <= 0 || key > pos_a - p.window);
           const bool ok_b = in_range && key <= pos_b && (p.window <= 0 || key > pos_b - p.window);
@@ -313,112 +302,66 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const Params p) 
           mx_b = fmaxf(mx_b, s[j][2 + e]);
         }
       }
-      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-      const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-      const float al_a = (mn_a == -INFINITY) ? 1.f : exp2f(m_a - mn_a);
-      const float al_b = (mn_b == -INFINITY) ? 1.f : exp2f(m_b - mn_b);
-      m_a = mn_a; m_b = mn_b;
-      float sum_a = 0.f, sum_b = 0.f;
-      uint32_t pa[NT][2];   // probabilities as bfloat16 pairs: [j][0] rows g, [j][1] rows g+8
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float use_a = (mn_a == -INFINITY) ? 0.f : mn_a, use_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+    const float al_a = ex2(m_a - use_a), al_b = ex2(m_b - use_b);   // ex2(-inf) = 0: nothing was accumulated yet
+    m_a = mn_a; m_b = mn_b;
+    float sum_a = 0.f, sum_b = 0.f;
+    uint32_t pa[NT][2];
 #pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        const float p0_ = (s[j][0] == -INFINITY) ? 0.f : exp2f(s[j][0] - mn_a);
-        const float p1_ = (s[j][1] == -INFINITY) ? 0.f : exp2f(s[j][1] - mn_a);
-        const float p2_ = (s[j][2] == -INFINITY) ? 0.f : exp2f(s[j][2] - mn_b);
-        const float p3_ = (s[j][3] == -INFINITY) ? 0.f : exp2f(s[j][3] - mn_b);
-        sum_a += p0_ + p1_;
-        sum_b += p2_ + p3_;
-        pa[j][0] = pack_bf16(p0_, p1_);
-        pa[j][1] = pack_bf16(p2_, p3_);
-      }
-      l_a = l_a * al_a + sum_a;   // per-thread partial sums; the four threads of a row are added at the end
-      l_b = l_b * al_b + sum_b;
+    for (int j = 0; j < NT; ++j) {
+      const float p0_ = ex2(s[j][0] - use_a), p1_ = ex2(s[j][1] - use_a);
+      const float p2_ = ex2(s[j][2] - use_b), p3_ = ex2(s[j][3] - use_b);
+      sum_a += p0_ + p1_;
+      sum_b += p2_ + p3_;
+      pa[j][0] = pack_bf16(p0_, p1_);
+      pa[j][1] = pack_bf16(p2_, p3_);
+    }
+    l_a = l_a * al_a + sum_a;
+    l_b = l_b * al_b + sum_b;
+    if (__any_sync(0xffffffffu, al_a != 1.f || al_b != 1.f)) {
 #pragma unroll
       for (int i = 0; i < D / 8; ++i) {
         o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
       }
-      // O += P V, 16 keys a step
+    }
 #pragma unroll
-      for (int ks = 0; ks < KW / 16; ++ks) {
-        const uint32_t a0 = pa[2 * ks][0], a1 = pa[2 * ks][1], a2 = pa[2 * ks + 1][0], a3 = pa[2 * ks + 1][1];
+    for (int ks = 0; ks < BN / 16; ++ks) {
 #pragma unroll
-        for (int i = 0; i < D / 8; i += 2) {
-          uint32_t b0, b1, b2, b3;   // (keys lo, d i*8..), (keys hi, d i*8..), (keys lo, d (i+1)*8..), (keys hi, d (i+1)*8..)
-          ldmatrix_x4_trans(b0, b1, b2, b3, Vs + (wn * KW + ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + i * 8 + (lane >> 4) * 8);
-          mma_bf16(o[i], a0, a1, a2, a3, b0, b1);
-          mma_bf16(o[i + 1], a0, a1, a2, a3, b2, b3);
-        }
+      for (int i = 0; i < D / 8; i += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, Vs + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + i * 8 + (lane >> 4) * 8);
+        mma_bf16(o[i], pa[2 * ks][0], pa[2 * ks][1], pa[2 * ks + 1][0], pa[2 * ks + 1][1], b0, b1);
+        mma_bf16(o[i + 1], pa[2 * ks][0], pa[2 * ks][1], pa[2 * ks + 1][0], pa[2 * ks + 1][1], b2, b3);
       }
     }
     __syncthreads();   // the stage may be overwritten by the next iteration's fetch
   }
-
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-
-  if (!DEEP) {
-    const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
-    if (row_a < M) {
-      const int tok = row_a / G, hd = hk * G + (row_a - tok * G);
-      bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)hd * D + tq * 2;
+  const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+  if (row_a < M) {
+    const int tok = row_a / G, hd = hk * G + (row_a - tok * G);
+    bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)hd * D + tq * 2;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][0] * inv_a, o[i][1] * inv_a);
-    }
-    if (row_b < M) {
-      const int tok = row_b / G, hd = hk * G + (row_b - tok * G);
-      bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)hd * D + tq * 2;
+    for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][0] * inv_a, o[i][1] * inv_a);
+  }
+  if (row_b < M) {
+    const int tok = row_b / G, hd = hk * G + (row_b - tok * G);
+    bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)hd * D + tq * 2;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2] * inv_b, o[i][3] * inv_b);
-    }
-    return;
-  } else {
-    // merge the four warps (each saw other keys) through shared memory, in float
-    float* Om = reinterpret_cast<float*>(smem_raw);           // [4][16][D]  (the stages are free now)
-    float* MLm = Om + 4 * 16 * D;                             // [4][16][2]
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      float* d0 = Om + ((size_t)warp * 16 + g) * D + i * 8 + tq * 2;
-      float* d1 = Om + ((size_t)warp * 16 + g + 8) * D + i * 8 + tq * 2;
-      d0[0] = o[i][0]; d0[1] = o[i][1];
-      d1[0] = o[i][2]; d1[1] = o[i][3];
-    }
-    if (tq == 0) {
-      MLm[(warp * 16 + g) * 2] = m_a;      MLm[(warp * 16 + g) * 2 + 1] = l_a;
-      MLm[(warp * 16 + g + 8) * 2] = m_b;  MLm[(warp * 16 + g + 8) * 2 + 1] = l_b;
-    }
-    __syncthreads();
-    const bool last = p.num_splits == 1;
-    for (int idx = tid; idx < 16 * D; idx += THREADS) {
-      const int row = idx / D, d = idx - row * D;
-      if (row >= M) continue;
-      float mm = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, MLm[(w * 16 + row) * 2]);
-      float ll = 0.f, acc = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float mw = MLm[(w * 16 + row) * 2];
-        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-        ll += MLm[(w * 16 + row) * 2 + 1] * f;
-        acc += Om[((size_t)w * 16 + row) * D + d] * f;
-      }
-      if (last) {
-        const int tok = row / G, hd = hk * G + (row - tok * G);
-        p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
-      } else {
-        const size_t base = (((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + row;
-        p.part_o[base * D + d] = acc;
-        if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
-      }
-    }
-    if (!last) finish_split(p, r, hk, q0, M, THREADS, reinterpret_cast<float*>(smem_raw));
+    for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2] * inv_b, o[i][3] * inv_b);
   }
 }
+
+size_t wide_smem_bytes() { return (size_t)(64 + 2 * 2 * BN) * LDS * sizeof(bf16); }
 
 // The deep shape, for requests with at most 16 rows (decoding). grid (splits, Hkv, R), 4 warps. The keys of the
 // block's split are dealt to the warps in sub-tiles of DKW (warp w takes sub-tiles w, w+4, ...); every warp runs
@@ -432,12 +375,6 @@ constexpr int DNT = DKW / 8;                              // score n-tiles per s
 constexpr int DSTAGES = D <= 128 ? 3 : 2;                 // steps in flight per warp
 constexpr bool DQ_IN_REGS = D <= 128;                     // query fragments live in registers
 constexpr int DCOPIES = DKW * CHUNKS / 32;                // 16-byte copies per lane per sub-tile and tensor
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 // Sub-tile of keys [k0, k0 + DKW) of kv head hk -> one stage. Keys outside [lo, hi) become zeros.
 __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, int bt_first, int hk, int k0, int lo, int hi,
@@ -753,12 +690,6 @@ __global__ void __launch_bounds__(THREADS) attention_merge_kernel(const Params p
   merge_splits(p, r, hk, q0, M, THREADS, work);
 }
 
-template <int WM, int WN> size_t smem_bytes() {
-  const size_t tiles = (size_t)(WM * 16 + stages_for(WN > 1) * 2 * BN) * LDS * sizeof(bf16);
-  const size_t merge = WN > 1 ? (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float) : 0;
-  return tiles > merge ? tiles : merge;
-}
-
 }  // namespace
 
 SB_EXPORT int sb_attention_mma_head_dim() { return D; }
@@ -787,8 +718,8 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
   p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   if (which & 1) {
-    auto k = attention_mma_kernel<4, 1>;
-    const size_t smem = smem_bytes<4, 1>();
+    auto k = attention_wide_kernel;
+    const size_t smem = wide_smem_bytes();
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const long long tiles = ((long long)max_q * p.G + 63) / 64;
     if (tiles > 2147483647LL) return SB_ERR_LIMIT;

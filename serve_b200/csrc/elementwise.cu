@@ -204,11 +204,40 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
+// bfloat16, 8 elements (16 bytes of gate, 16 of up) per thread; needs inter % 8 == 0 and aligned pointers
+__global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter8,
+                                       size_t total8) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter8;
+    const int i = (int)(idx - t * inter8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + (t * 2 * inter8 + i) * 8);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + (t * 2 * inter8 + inter8 + i) * 8);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = ov;
+  }
+}
+
 SB_EXPORT int sb_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (inter <= 0) return SB_ERR_SHAPE;
   const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
+  if (dtype == SB_DTYPE_BF16 && (inter % 8) == 0 && aligned16(gate_up) && aligned16(out)) {
+    const size_t total8 = total / 8;
+    const size_t want = (total8 + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    swiglu_bf16_vec_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter / 8, total8);
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == SB_DTYPE_F32)
     swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
