@@ -171,7 +171,16 @@ def e2e_bench(eng, batch, steps, vocab, seed):
 
 
 def reference_arm(args):
-    print(json.dumps({"impl": "reference", "unavailable": "limei1221/serve is not installed under baseline/_ref on this box"}))
+    """The reference's own benchmark would run here from baseline/_ref. Its offline install fails on this image:
+    `pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref <reference>` stops
+    with "ModuleNotFoundError: No module named 'hatchling'" (the build backend its pyproject.toml names is neither
+    installed nor in the wheelhouse), also from a writable copy and with --no-deps."""
+    installed = os.path.isfile(os.path.join(ROOT, "baseline", "_ref", "serve", "run.py"))
+    why = ("limei1221/serve cannot be installed offline here: its build backend 'hatchling' is neither installed nor in "
+           "/opt/wheelhouse (pip: No module named 'hatchling')")
+    if installed:
+        why = "baseline/_ref holds the reference, but no runner for it was built because the install failed when bench.py was written"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
