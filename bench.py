@@ -94,7 +94,7 @@ def model_bytes_and_flops(cfg, dtype_bytes):
     return weights, kv_per_token, prefill_flops
 
 
-def decode_bench(eng, sampler, batch, steps, warmup, vocab, seed):
+def decode_bench(eng, sampler, batch, steps, warmup, vocab, seed, cuda_profiler=False):
     """Prefill ``batch`` prompts of PROMPT_LEN tokens, then time ``steps`` decode steps on the device."""
     import torch
     from serve_b200.engine import StepEntry
@@ -117,11 +117,15 @@ def decode_bench(eng, sampler, batch, steps, warmup, vocab, seed):
     k = eng.kernels
     l0, c0 = k.launches, k.library_calls
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if cuda_profiler:
+        torch.cuda.profiler.start()
     ev0.record()
     for i in range(warmup, warmup + steps):
         one(i)
     ev1.record()
     torch.cuda.synchronize()
+    if cuda_profiler:
+        torch.cuda.profiler.stop()
     ms = ev0.elapsed_time(ev1) / steps
     ctx_mid = PROMPT_LEN + warmup + steps / 2.0
     for rid in rids:
@@ -129,7 +133,7 @@ def decode_bench(eng, sampler, batch, steps, warmup, vocab, seed):
     return ms, ctx_mid, k.launches - l0, k.library_calls - c0
 
 
-def prefill_bench(eng, vocab, reps, seed):
+def prefill_bench(eng, vocab, reps, seed, cuda_profiler=False):
     import torch
     from serve_b200.engine import StepEntry
 
@@ -139,10 +143,14 @@ def prefill_bench(eng, vocab, reps, seed):
         toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
         torch.cuda.synchronize()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if cuda_profiler and i == reps + 1:
+            torch.cuda.profiler.start()
         ev0.record()
         eng.step([StepEntry(f"p{i}", toks, [PREFILL_TOKENS - 1])])
         ev1.record()
         torch.cuda.synchronize()
+        if cuda_profiler and i == reps + 1:
+            torch.cuda.profiler.stop()
         eng.end(f"p{i}")
         if i >= 2:
             times.append(ev0.elapsed_time(ev1))
@@ -193,6 +201,10 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in the record)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for per-kernel profiles)")
+    ap.add_argument("--cuda-profiler", action="store_true",
+                    help="bracket the timed region with cudaProfilerStart/Stop (ncu --profile-from-start off)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None, help="measure just this part (for profiles)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (use --gpus 1)")
@@ -215,16 +227,25 @@ def main():
     page = 64
     max_batch = max(64, args.batch)
     ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=max_batch * CONTEXT // page + 64, max_slots=max_batch + 2,
-                      max_tokens_per_step=max(PROMPT_LEN, PREFILL_TOKENS), max_context=CONTEXT)
+                      max_tokens_per_step=max(PROMPT_LEN, PREFILL_TOKENS), max_context=CONTEXT,
+                      use_cuda_graphs=not args.no_graphs)
     with torch.inference_mode():
         eng = Engine.from_config(cfg, seed=0, engine_config=ec)
         sampler = Sampler(eng.kernels, eng.rt.device, seed=0)
         weights, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, 2)
 
+        if args.only == "prefill":
+            pre_ms = prefill_bench(eng, cfg.vocab_size, reps=2, seed=7, cuda_profiler=args.cuda_profiler)
+            print(json.dumps({"only": "prefill", "ms": round(pre_ms, 3), "tokens": PREFILL_TOKENS}))
+            return 0
         clocks = ClockSampler()
         clocks.start()
-        ms, ctx_mid, launches, lib_calls = decode_bench(eng, sampler, args.batch, args.steps, args.warmup, cfg.vocab_size, seed=1)
+        ms, ctx_mid, launches, lib_calls = decode_bench(eng, sampler, args.batch, args.steps, args.warmup, cfg.vocab_size, seed=1,
+                                                        cuda_profiler=args.cuda_profiler)
         clock_rec = clocks.stop()
+        if args.only == "decode":
+            print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4), "graphs": not args.no_graphs}))
+            return 0
         value = args.batch * 1000.0 / ms
         step_bytes = weights + args.batch * ctx_mid * kv_per_token
         achieved = step_bytes / (ms * 1e-3) / 1e9

@@ -183,7 +183,7 @@ __device__ __forceinline__ float ex2(float x) {
 // position (and inside every row's window) skip the mask; the heaviest row tiles (the last ones) start first.
 constexpr bool WQ_IN_REGS = D <= 128;
 
-__global__ void __launch_bounds__(THREADS) attention_wide_kernel(const Params p) {
+__global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_kernel(const Params p) {
   constexpr int BM = 64;
   constexpr int NT = BN / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];

@@ -374,57 +374,85 @@ __device__ __forceinline__ float counter_uniform(uint32_t seed_lo, uint32_t seed
   return ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1)
 }
 
+// Order-preserving key of (score, index): a larger score gives a larger key, and among equal scores the lower
+// index does. Key 0 is below every real key.
+__device__ __forceinline__ unsigned long long sample_key(float s, int i) {
+  uint32_t u = __float_as_uint(s);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
+}
+
+// grid (rows, chunks): every block scans its share of the vocabulary and folds its best (score, index) into the
+// row's key with one atomicMax; the block that arrives last (a counter per row) turns the key into the token
+// and leaves key and counter zero for the next call. Nobody waits for anybody.
 __global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                               const int* __restrict__ req_ids, const int* __restrict__ tok_index, uint32_t seed_lo,
-                              uint32_t seed_hi, int vocab, int* __restrict__ out) {
-  __shared__ float sval[32];
-  __shared__ int sidx[32];
+                              uint32_t seed_hi, int vocab, int* __restrict__ out, unsigned long long* __restrict__ keys,
+                              int* __restrict__ counters) {
+  __shared__ unsigned long long skey[32];
   const int r = blockIdx.x;
   const float* lr = logits + (size_t)r * vocab;
   pdl_launch_dependents();
   pdl_wait();
   const float temp = temperature[r];
   const uint32_t req = (uint32_t)req_ids[r], tok = (uint32_t)tok_index[r];
-  float best = -INFINITY;
-  int besti = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  const int per = (vocab + gridDim.y - 1) / gridDim.y;
+  const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
+  unsigned long long best = 0ull;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     float s = lr[i];
     if (temp > 0.f) {
       const float u = counter_uniform(seed_lo, seed_hi, req, tok, (uint32_t)i);
       const float q = -logf(u);             // Exp(1)
       s = s / temp - logf(q);
     }
-    if (s > best || (s == best && i < besti)) { best = s; besti = i; }
+    if (s == s) {                           // a NaN is never chosen
+      const unsigned long long k = sample_key(s, i);
+      best = k > best ? k : best;
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-    if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { sval[warp] = best; sidx[warp] = besti; }
+  if (lane == 0) skey[warp] = best;
   __syncthreads();
   if (warp == 0) {
     const int nw = (blockDim.x + 31) >> 5;
-    best = lane < nw ? sval[lane] : -INFINITY;
-    besti = lane < nw ? sidx[lane] : 0x7fffffff;
+    best = lane < nw ? skey[lane] : 0ull;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-      if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
     }
-    if (lane == 0) out[r] = (besti == 0x7fffffff) ? 0 : besti;
+    if (lane == 0) {
+      if (best) atomicMax(keys + r, best);
+      __threadfence();
+      if (atomicAdd(counters + r, 1) == (int)gridDim.y - 1) {
+        __threadfence();
+        const unsigned long long k = atomicExch(keys + r, 0ull);
+        out[r] = k ? (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull)) : 0;
+        counters[r] = 0;
+      }
+    }
   }
 }
 
+// work: n_rows 64-bit keys followed by n_rows int counters (16-byte aligned), all zero before the first call;
+// every call leaves them zero.
 SB_EXPORT int sb_sample(const float* logits, const float* temperature, const int* req_ids, const int* tok_index,
-                        unsigned long long seed, int n_rows, int vocab, int* out, cudaStream_t stream) {
+                        unsigned long long seed, int n_rows, int vocab, int* out, void* work, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  if (vocab <= 0) return SB_ERR_SHAPE;
-  const int threads = vocab >= 4096 ? 1024 : 256;
-  SB_PDL_CHECK(launch_pdl(sample_kernel, dim3(n_rows), dim3(threads), 0, stream, logits, temperature, req_ids, tok_index,
-                          (uint32_t)(seed & 0xffffffffULL), (uint32_t)(seed >> 32), vocab, out));
+  if (vocab <= 0 || !work) return SB_ERR_SHAPE;
+  if (n_rows > 65535) return SB_ERR_LIMIT;
+  const int threads = 256;
+  int chunks = (vocab + 4095) / 4096;      // at least 16 values per thread
+  if (chunks > 64) chunks = 64;
+  unsigned long long* keys = (unsigned long long*)work;
+  int* counters = (int*)(keys + n_rows);
+  SB_PDL_CHECK(launch_pdl(sample_kernel, dim3(n_rows, chunks), dim3(threads), 0, stream, logits, temperature, req_ids, tok_index,
+                          (uint32_t)(seed & 0xffffffffULL), (uint32_t)(seed >> 32), vocab, out, keys, counters));
   return 0;
 }

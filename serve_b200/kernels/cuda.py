@@ -84,6 +84,8 @@ class CudaKernels:
         self._errors: Optional[torch.Tensor] = None
         self.force_simt_attention = False   # tests: run bfloat16 through the plain-arithmetic kernel
         self.use_skinny_linear = True       # tests: False sends every product to the library
+        self._sample_work = None
+        self._keep = []
         self._tickets = []                   # zeroed int32 buffers of the split-key merge (kept alive for graphs)
         self.launches = 0         # launches of this engine's own kernels
         self.library_calls = 0    # library matrix products
@@ -234,8 +236,13 @@ class CudaKernels:
 
     def sample(self, logits, temperature, req_ids, tok_index, seed, out) -> None:
         self.launches += 1
+        n = logits.shape[0]
+        if self._sample_work is None or self._sample_work.numel() < 3 * n:
+            # n 64-bit keys and n counters, zero now and after every call (kept alive for captured graphs)
+            self._sample_work = torch.zeros(3 * max(n, 256), dtype=torch.int32, device=self.device)
+            self._keep.append(self._sample_work)
         _check(self._core.sb_sample(_p(logits), _p(temperature), _p(req_ids), _p(tok_index), ctypes.c_ulonglong(seed),
-                                    logits.shape[0], logits.shape[1], _p(out), _stream()), "sample")
+                                    n, logits.shape[1], _p(out), _p(self._sample_work), _stream()), "sample")
 
 
 _INSTANCES: Dict[str, CudaKernels] = {}
