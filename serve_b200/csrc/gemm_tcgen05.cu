@@ -1,0 +1,281 @@
+// Matrix products for many rows (prompt portions) on the fifth-generation tensor cores:
+// out[M,N] = a[M,K] * w[N,K]^T, bfloat16 in, float accumulation in tensor memory, bfloat16 out.
+// With gate_up, w is [2N, K] (gate rows, then up rows) and out[m,n] = silu(gate) * up (serve/model.py:85):
+// the activation is applied while the accumulator leaves tensor memory, and the [M, 2N] intermediate of the
+// unfused path is never written.
+//
+// One CTA computes a 128 x 128 tile of the accumulator (with gate_up: 64 gate columns and their 64 up
+// columns). Warp 0 feeds a ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle, one
+// 128 x 64 box of a and one or two boxes of w per stage, completion counted on an mbarrier); one thread of
+// warp 1 issues tcgen05.mma (128 x 128 x 16, operands read from shared memory through matrix descriptors,
+// accumulator in tensor memory) and releases stages with tcgen05.commit; warps 2..5 read the accumulator back
+// with tcgen05.ld, apply the epilogue and store. Two CTAs fit an SM, so one tile's epilogue overlaps the
+// other's products. Rows beyond M and k-values beyond K are zero-filled by TMA; stores are guarded.
+//
+// Every wait is bounded; a wait that runs out raises *error, and the CTA still frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+using namespace sb;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;      // accumulator tile and k-values per stage
+constexpr int NSTAGE = 3;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;                     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
+constexpr unsigned WAIT_LIMIT = 1u << 26;
+constexpr uint32_t TMEM_COLS = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 columns of 32-bit accumulator: thread i of the warp gets lane (base lane + i), 32 consecutive columns
+__device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored by TMA with the 128-byte swizzle: rows of 128 bytes,
+// 8 rows to a 1024-byte atom, atoms one after the other (stride 1024 bytes); version 1, layout type 2.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);            // start address, 16-byte units
+  d |= (uint64_t)0 << 16;                                 // leading byte offset: not used by this layout
+  d |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                                 // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                                 // 128-byte swizzle
+  return d;
+}
+
+// kind::f16 instruction descriptor: float accumulator, bfloat16 a and b, both K-major, N x M of the tile
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <bool GU>
+__global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_w, bf16* __restrict__ out,
+                                                               int M, int N, int K, int* __restrict__ error) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[NSTAGE];
+  __shared__ __align__(8) uint64_t empty_bar[NSTAGE];
+  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ uint32_t tmem_base_s;
+  // the dynamic region is aligned by hand: the 128-byte swizzle wants 1024-byte aligned tiles
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int OUT_COLS = GU ? BN / 2 : BN;         // output columns of one tile
+  const int m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * OUT_COLS;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % NSTAGE;
+        // a fresh barrier passes a wait on parity 1: the first round finds every stage free
+        if (!mbar_wait(&empty_bar[s], ((kb / NSTAGE) & 1) ^ 1)) { failed = true; break; }
+        unsigned char* a_dst = tiles + (size_t)s * STAGE_BYTES;
+        unsigned char* b_dst = a_dst + A_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
+        if (GU) {
+          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);                       // 64 gate rows
+          tma_load_2d(b_dst + B_BYTES / 2, &map_w, &full_bar[s], kb * BK, N + n0);     // their 64 up rows
+        } else {
+          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % NSTAGE;
+        if (!mbar_wait(&full_bar[s], (kb / NSTAGE) & 1)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+        const uint64_t da = make_desc(a_addr), db = make_desc(a_addr + A_BYTES);
+#pragma unroll
+        for (int j = 0; j < BK / 16; ++j) {
+          // 16 k-values further along the swizzled row: 32 bytes, two 16-byte units of the start address
+          tc_mma(tmem_base, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kb | j) != 0 ? 1u : 0u);
+        }
+        tc_commit(&empty_bar[s]);          // the stage is free once these products have read it
+      }
+      tc_commit(&acc_bar);                 // the accumulator is complete once all products are done
+    }
+  } else {
+    // epilogue warps 2..5: a warp may touch the 32 tensor-memory lanes of its rank modulo 4
+    const int q = warp & 3;
+    if (!mbar_wait(&acc_bar, 0)) failed = true;
+    tc_fence_after();
+    const int row = m0 + q * 32 + lane;
+    if (!failed) {
+#pragma unroll 1
+      for (int c = 0; c < OUT_COLS; c += 32) {
+        uint32_t v[32];
+        tc_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+        uint32_t packed[16];
+        if (GU) {
+          uint32_t u[32];
+          tc_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(OUT_COLS + c), u);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // both halves rounded to the activation type first, as the unfused path stores them
+            const float g0 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i]))), g1 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i + 1])));
+            const float u0 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i]))), u1 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i + 1])));
+            __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            packed[i] = *reinterpret_cast<uint32_t*>(&o);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            packed[i] = *reinterpret_cast<uint32_t*>(&o);
+          }
+        }
+        if (row < M) {
+          bf16* dst = out + (size_t)row * N + n0 + c;
+          if (n0 + c + 32 <= N && (N % 8) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (n0 + c + i < N) dst[i] = reinterpret_cast<const bf16*>(packed)[i];
+          }
+        }
+      }
+    }
+  }
+  if (failed) atomicExch(error, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// rows x cols bfloat16, row-major; box of box_rows x 64 columns, 128-byte swizzle, zero fill outside
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) return -300;
+    g_encode = (EncodeTiledFn)fn;
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -301 - (int)r;
+}
+
+}  // namespace
+
+// 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).
+SB_EXPORT int sb_gemm_tcgen05_supports(int M, int N, int K, int gate_up) {
+  if (M < 1 || N < 8 || K < 8 || (K % 8) || (N % 8)) return 0;     // 16-byte row pitch for TMA, vector stores
+  if (gate_up && (N % 64)) return 0;                                // a tile's gate and up rows must not straddle
+  return 1;
+}
+
+// a [M,K], w [N,K] (or [2N,K] with gate_up), out [M,N]; all bfloat16, row-major, 16-byte aligned.
+// error: device int set to 1 if a bounded wait inside the kernel ran out.
+SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int gate_up, int* error,
+                              cudaStream_t stream) {
+  if (!sb_gemm_tcgen05_supports(M, N, K, gate_up)) return SB_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(w) || !aligned16(out) || !error) return SB_ERR_ALIGN;
+  CUtensorMap map_a, map_w;
+  int rc = make_map(&map_a, a, (uint64_t)M, (uint64_t)K, BM);
+  if (rc) return rc;
+  rc = make_map(&map_w, w, (uint64_t)(gate_up ? 2 * N : N), (uint64_t)K, gate_up ? BN / 2 : BN);
+  if (rc) return rc;
+  const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 1024;
+  const int out_cols = gate_up ? BN / 2 : BN;
+  dim3 grid((N + out_cols - 1) / out_cols, (M + BM - 1) / BM);
+  if (gate_up) {
+    auto k = gemm_tcgen05_kernel<true>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, error);
+  } else {
+    auto k = gemm_tcgen05_kernel<false>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, error);
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}

@@ -46,7 +46,7 @@ def _stream():
 
 def core_jobs():
     return [
-        {"name": "sb_core", "sources": ["elementwise.cu", "skinny_linear.cu"]},
+        {"name": "sb_core", "sources": ["elementwise.cu", "skinny_linear.cu", "gemm_tcgen05.cu"]},
         {"name": "sb_gemm", "sources": ["gemm_cublas.cu"], "libs": ["cublas"]},
     ]
 
@@ -84,6 +84,7 @@ class CudaKernels:
         self._errors: Optional[torch.Tensor] = None
         self.force_simt_attention = False   # tests: run bfloat16 through the plain-arithmetic kernel
         self.use_skinny_linear = True       # tests: False sends every product to the library
+        self.use_tcgen05 = True             # tests: False keeps many-row products in the library
         self._sample_work = None
         self._keep = []
         self._tickets = []                   # zeroed int32 buffers of the split-key merge (kept alive for graphs)
@@ -114,15 +115,23 @@ class CudaKernels:
 
     def errors_tensor(self) -> torch.Tensor:
         if self._errors is None:
-            self._errors = torch.zeros(1, dtype=torch.int32, device=self.device)
+            # [0]: cache writes that met a missing page; [1]: a bounded wait inside a kernel ran out
+            self._errors = torch.zeros(4, dtype=torch.int32, device=self.device)
         return self._errors
+
+    TCGEN05_MIN_ROWS = 64   # fewer rows than this leave most of a 128-row tile empty
+
+    def _wait_flag(self):
+        return ctypes.c_void_p(self.errors_tensor().data_ptr() + 4)
 
     def check_errors(self) -> None:
         """Raise if a kernel met a page id or block index outside its table (synchronises)."""
         if self._errors is not None:
-            n = int(self._errors.item())
-            if n:
+            n, timeouts = self._errors[:2].tolist()
+            if n or timeouts:
                 self._errors.zero_()
+                if timeouts:
+                    raise KernelError("a wait on a copy or tensor-core barrier inside a kernel ran out; the step's results are not valid")
                 raise KernelError(f"{n} cache writes met a missing page or a block index beyond the block table")
 
     # ---- kernels ----------------------------------------------------------
@@ -150,6 +159,11 @@ class CudaKernels:
             self.launches += 1
             _check(self._core.sb_skinny_linear(_p(a), _p(w), _p(out), m, n, k, _DT[out.dtype], 0, _stream()), "skinny linear")
             return
+        if (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self.use_tcgen05 and m >= self.TCGEN05_MIN_ROWS
+                and self._core.sb_gemm_tcgen05_supports(m, n, k, 0)):
+            self.launches += 1
+            _check(self._core.sb_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, 0, self._wait_flag(), _stream()), "tcgen05 product")
+            return
         self.library_calls += 1
         _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), m, n, k, _DT[a.dtype], _DT[out.dtype], _stream()), "linear")
 
@@ -162,6 +176,12 @@ class CudaKernels:
             self.launches += 1
             _check(self._core.sb_skinny_linear(_p(h), _p(w_gate_up), _p(out), t, inter, k, _DT[out.dtype], 1, _stream()),
                    "skinny gate/up")
+            return
+        if (h.dtype == torch.bfloat16 and self.use_tcgen05 and t >= self.TCGEN05_MIN_ROWS
+                and self._core.sb_gemm_tcgen05_supports(t, inter, k, 1)):
+            self.launches += 1
+            _check(self._core.sb_gemm_tcgen05(_p(h), _p(w_gate_up), _p(out), t, inter, k, 1, self._wait_flag(), _stream()),
+                   "tcgen05 gate/up")
             return
         gate_up = torch.empty((t, 2 * inter), dtype=h.dtype, device=h.device)
         self.linear(h, w_gate_up, gate_up)

@@ -61,12 +61,15 @@ def main(argv=None) -> int:
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--graph", action="store_true")
+    ap.add_argument("--library", action="store_true", help="send products to the library (cuBLAS) instead of this engine's kernels")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
     from .cuda import load_kernels
 
     dev = a.device
     K = load_kernels(dev, head_dims=(a.head_dim,))
+    if a.library:
+        K.use_tcgen05 = K.use_skinny_linear = False
     bf = torch.bfloat16
     if a.kernel in ("linear", "gate_up"):
         rows = 2 * a.n if a.kernel == "gate_up" else a.n
