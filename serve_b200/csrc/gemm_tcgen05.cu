@@ -4,13 +4,15 @@
 // the activation is applied while the accumulator leaves tensor memory, and the [M, 2N] intermediate of the
 // unfused path is never written.
 //
-// One CTA computes a 128 x 128 tile of the accumulator (with gate_up: 64 gate columns and their 64 up
-// columns). Warp 0 feeds a ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle, one
-// 128 x 64 box of a and one or two boxes of w per stage, completion counted on an mbarrier); one thread of
-// warp 1 issues tcgen05.mma (128 x 128 x 16, operands read from shared memory through matrix descriptors,
-// accumulator in tensor memory) and releases stages with tcgen05.commit; warps 2..5 read the accumulator back
-// with tcgen05.ld, apply the epilogue and store. Two CTAs fit an SM, so one tile's epilogue overlaps the
-// other's products. Rows beyond M and k-values beyond K are zero-filled by TMA; stores are guarded.
+// A persistent CTA per SM walks over 128 x 256 tiles of the accumulator (with gate_up: 128 gate columns and
+// their 128 up columns, i.e. 128 output columns). Warp 0 feeds a ring of four shared-memory stages with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle: one 128 x 64 box of a and a 256 x 64 box, or two 128 x 64 boxes, of
+// w per stage, completion counted on an mbarrier); one thread of warp 1 issues tcgen05.mma (128 x 256 x 16,
+// operands read from shared memory through matrix descriptors, accumulator in tensor memory) and releases
+// stages with tcgen05.commit; warps 2..5 read a finished accumulator back with tcgen05.ld, apply the epilogue
+// and store. Tensor memory holds two accumulators (2 x 256 columns), so the epilogue of one tile runs while
+// the products of the next are issued. Tiles that share a panel of w run at the same time on neighbouring
+// CTAs, so w comes from HBM once. Rows beyond M and k-values beyond K are zero-filled by TMA; stores are guarded.
 //
 // Every wait is bounded; a wait that runs out raises *error, and the CTA still frees its tensor memory.
 #include <cuda.h>
@@ -22,12 +24,12 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;      // accumulator tile and k-values per stage
-constexpr int NSTAGE = 3;
+constexpr int BM = 128, BN = 256, BK = 64;      // accumulator tile and k-values per stage
+constexpr int NSTAGE = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;                     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
 constexpr unsigned WAIT_LIMIT = 1u << 26;
-constexpr uint32_t TMEM_COLS = 128;
+constexpr uint32_t TMEM_COLS = 512;              // two accumulators of BN columns
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
@@ -95,19 +97,22 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
 template <bool GU>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w, bf16* __restrict__ out,
-                                                               int M, int N, int K, int* __restrict__ error) {
+                                                               int M, int N, int K, int bn, int* __restrict__ error) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[NSTAGE];
   __shared__ __align__(8) uint64_t empty_bar[NSTAGE];
-  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   // the dynamic region is aligned by hand: the 128-byte swizzle wants 1024-byte aligned tiles
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int OUT_COLS = GU ? BN / 2 : BN;         // output columns of one tile
-  const int m0 = blockIdx.y * BM;
-  const int n0 = blockIdx.x * OUT_COLS;
+  // bn: accumulator columns of a tile (a multiple of 32, at most BN), chosen by the host so that the tiles
+  // fill whole waves of CTAs
+  const int OUT_COLS = GU ? bn / 2 : bn;             // output columns of one tile
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + OUT_COLS - 1) / OUT_COLS;
+  const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -116,7 +121,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&acc_bar, 1);
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);       // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -132,57 +141,75 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   const uint32_t tmem_base = tmem_base_s;
   bool failed = false;
 
+  // tile t of this CTA: consecutive CTAs take the row tiles of one panel of w
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % NSTAGE;
-        // a fresh barrier passes a wait on parity 1: the first round finds every stage free
-        if (!mbar_wait(&empty_bar[s], ((kb / NSTAGE) & 1) ^ 1)) { failed = true; break; }
-        unsigned char* a_dst = tiles + (size_t)s * STAGE_BYTES;
-        unsigned char* b_dst = a_dst + A_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
-        if (GU) {
-          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);                       // 64 gate rows
-          tma_load_2d(b_dst + B_BYTES / 2, &map_w, &full_bar[s], kb * BK, N + n0);     // their 64 up rows
-        } else {
-          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
+      int it = 0;                                      // stages issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          // a fresh barrier passes a wait on parity 1: the first round finds every stage free
+          if (!mbar_wait(&empty_bar[s], ((it / NSTAGE) & 1) ^ 1)) { failed = true; break; }
+          unsigned char* a_dst = tiles + (size_t)s * STAGE_BYTES;
+          unsigned char* b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(&full_bar[s], (unsigned)(A_BYTES + bn * BK * 2));
+          tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
+          if (GU) {
+            tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);                       // 128 gate rows
+            tma_load_2d(b_dst + (size_t)(bn / 2) * BK * 2, &map_w, &full_bar[s], kb * BK, N + n0);   // their up rows
+          } else {
+            tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % NSTAGE;
-        if (!mbar_wait(&full_bar[s], (kb / NSTAGE) & 1)) { failed = true; break; }
+      const uint32_t idesc = make_idesc(BM, bn);
+      int it = 0, local = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // the epilogue must have emptied this accumulator (first use of each: passes at once)
+        if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1)) { failed = true; break; }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-        const uint64_t da = make_desc(a_addr), db = make_desc(a_addr + A_BYTES);
+        const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          if (!mbar_wait(&full_bar[s], (it / NSTAGE) & 1)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t da = make_desc(a_addr), db = make_desc(a_addr + A_BYTES);
 #pragma unroll
-        for (int j = 0; j < BK / 16; ++j) {
-          // 16 k-values further along the swizzled row: 32 bytes, two 16-byte units of the start address
-          tc_mma(tmem_base, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kb | j) != 0 ? 1u : 0u);
+          for (int j = 0; j < BK / 16; ++j) {
+            // 16 k-values further along the swizzled row: 32 bytes, two 16-byte units of the start address
+            tc_mma(acc, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);          // the stage is free once these products have read it
         }
-        tc_commit(&empty_bar[s]);          // the stage is free once these products have read it
+        tc_commit(&acc_full[buf]);           // the accumulator is complete once all products are done
       }
-      tc_commit(&acc_bar);                 // the accumulator is complete once all products are done
     }
   } else {
     // epilogue warps 2..5: a warp may touch the 32 tensor-memory lanes of its rank modulo 4
     const int q = warp & 3;
-    if (!mbar_wait(&acc_bar, 0)) failed = true;
-    tc_fence_after();
-    const int row = m0 + q * 32 + lane;
-    if (!failed) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
+      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
+      const int buf = local & 1;
+      if (!mbar_wait(&acc_full[buf], (local >> 1) & 1)) { failed = true; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
       for (int c = 0; c < OUT_COLS; c += 32) {
+        if (n0 + c >= N) break;
         uint32_t v[32];
-        tc_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+        tc_load32(acc + (uint32_t)c, v);
         uint32_t packed[16];
         if (GU) {
           uint32_t u[32];
-          tc_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(OUT_COLS + c), u);
+          tc_load32(acc + (uint32_t)(OUT_COLS + c), u);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             // both halves rounded to the activation type first, as the unfused path stores them
@@ -200,7 +227,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
         }
         if (row < M) {
           bf16* dst = out + (size_t)row * N + n0 + c;
-          if (n0 + c + 32 <= N && (N % 8) == 0) {
+          if (n0 + c + 32 <= N) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
               *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
@@ -210,6 +237,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
           }
         }
       }
+      // this warp has read its part of the accumulator: the next tile but one may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
     }
   }
   if (failed) atomicExch(error, 1);
@@ -249,7 +280,7 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
 // 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).
 SB_EXPORT int sb_gemm_tcgen05_supports(int M, int N, int K, int gate_up) {
   if (M < 1 || N < 8 || K < 8 || (K % 8) || (N % 8)) return 0;     // 16-byte row pitch for TMA, vector stores
-  if (gate_up && (N % 64)) return 0;                                // a tile's gate and up rows must not straddle
+  if (gate_up && (N % 128)) return 0;                               // a tile's 128 gate rows must not reach into the up rows
   return 1;
 }
 
@@ -262,19 +293,38 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
   CUtensorMap map_a, map_w;
   int rc = make_map(&map_a, a, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
-  rc = make_map(&map_w, w, (uint64_t)(gate_up ? 2 * N : N), (uint64_t)K, gate_up ? BN / 2 : BN);
+  int sms = 148;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  // accumulator columns per tile: the width whose tiles need the least time in whole waves of one CTA per SM
+  // (time of a wave ~ tile width, plus a fixed part of about 32 columns' worth)
+  const long long m_tiles = (M + BM - 1) / BM;
+  int bn = BN;
+  if (!gate_up) {
+    long long best = -1;
+    for (int cand = BN; cand >= 128; cand -= 32) {
+      const long long n_tiles = (N + cand - 1) / cand;
+      const long long waves = (m_tiles * n_tiles + sms - 1) / sms;
+      const long long cost = waves * (cand + 32);
+      if (best < 0 || cost < best) { best = cost; bn = cand; }
+    }
+  }
+  rc = make_map(&map_w, w, (uint64_t)(gate_up ? 2 * N : N), (uint64_t)K, gate_up ? bn / 2 : bn);
   if (rc) return rc;
   const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 1024;
-  const int out_cols = gate_up ? BN / 2 : BN;
-  dim3 grid((N + out_cols - 1) / out_cols, (M + BM - 1) / BM);
+  const int out_cols = gate_up ? bn / 2 : bn;
+  const long long tiles = (long long)((N + out_cols - 1) / out_cols) * m_tiles;
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   if (gate_up) {
     auto k = gemm_tcgen05_kernel<true>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, error);
+    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
   } else {
     auto k = gemm_tcgen05_kernel<false>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, error);
+    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
   }
   SB_LAUNCH_CHECK();
   return 0;

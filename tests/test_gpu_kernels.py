@@ -391,3 +391,61 @@ def test_sizes_the_skinny_kernel_leaves_to_the_library(K):
         out = torch.empty(m, n, device=DEV)
         K.linear(a, w, out)
         torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=1e-2, rtol=1e-3)
+
+
+TC_SHAPES = [(128, 128, 64), (256, 256, 256), (2048, 3072, 2048), (300, 264, 200), (64, 136, 72), (1000, 2048, 8192), (129, 8, 8)]
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES)
+def test_tcgen05_product(K, m, n, k):
+    """The tensor-memory product (TMA in, tcgen05.mma, tcgen05.ld out) against float64: full tiles, ragged edges in every
+    dimension, k not a multiple of the stage, a single partial tile."""
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+    assert K._core.sb_gemm_tcgen05_supports(m, n, k, 0) == 1
+    before = K.launches
+    K.linear(a, w, out)
+    assert K.launches == before + 1, "these sizes must take the hand-written kernel"
+    K.check_errors()
+    ref = a.double() @ w.double().T
+    assert bool(torch.isfinite(out.float()).all()), "a tile was not written"
+    torch.testing.assert_close(out.double(), ref, atol=float(ref.abs().max()) * 2.0 ** -7, rtol=0)
+    # the library agrees, and a row's result does not depend on the other rows of the step
+    K.use_tcgen05 = False
+    try:
+        lib = torch.empty_like(out)
+        K.linear(a, w, lib)
+    finally:
+        K.use_tcgen05 = True
+    torch.testing.assert_close(out.float(), lib.float(), atol=float(ref.abs().max()) * 2.0 ** -7, rtol=0)
+    if m > 64:
+        part = torch.empty(64, n, device=DEV, dtype=torch.bfloat16)
+        K.linear(a[m - 64:].contiguous(), w, part)
+        assert torch.equal(part, out[m - 64:])
+
+
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (2048, 8192, 2048), (300, 384, 200), (130, 128, 72), (64, 256, 96)])
+def test_tcgen05_gate_up_with_swiglu(K, m, inter, k):
+    h = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=DEV) * 0.05).to(torch.bfloat16)
+    fused = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    assert K._core.sb_gemm_tcgen05_supports(m, inter, k, 1) == 1
+    K.gate_up_swiglu(h, w, fused)
+    K.check_errors()
+    ref = torch.empty_like(fused)
+    E.gate_up_swiglu(h, w, ref)
+    scale = float(ref.float().abs().max())
+    assert bool(torch.isfinite(fused.float()).all())
+    torch.testing.assert_close(fused.float(), ref.float(), atol=scale * 2.0 ** -6, rtol=0)
+
+
+def test_sizes_the_tcgen05_product_leaves_to_the_library(K):
+    assert K._core.sb_gemm_tcgen05_supports(128, 100, 64, 0) == 0      # output rows must be 16-byte multiples
+    assert K._core.sb_gemm_tcgen05_supports(128, 128, 60, 0) == 0      # so must input rows (TMA pitch)
+    assert K._core.sb_gemm_tcgen05_supports(128, 192, 64, 1) == 0      # gate tile would reach into the up rows
+    a = torch.randn(128, 60, device=DEV).to(torch.bfloat16)
+    w = torch.randn(100, 60, device=DEV).to(torch.bfloat16)
+    out = torch.empty(128, 100, device=DEV, dtype=torch.bfloat16)
+    K.linear(a, w, out)
+    torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=0.3, rtol=2e-2)
