@@ -119,7 +119,12 @@ class CudaKernels:
             self._errors = torch.zeros(4, dtype=torch.int32, device=self.device)
         return self._errors
 
-    TCGEN05_MIN_ROWS = 64   # fewer rows than this leave most of a 128-row tile empty
+    # The tensor-memory product works in 128 x 256 tiles, one CTA per SM: with fewer tiles than this most SMs
+    # would idle and the library's split-k kernels are the better choice.
+    TCGEN05_MIN_TILES = 96
+
+    def _tcgen05_worthwhile(self, m: int, n_acc: int) -> bool:
+        return self.use_tcgen05 and (-(-m // 128)) * (-(-n_acc // 256)) >= self.TCGEN05_MIN_TILES
 
     def _wait_flag(self):
         return ctypes.c_void_p(self.errors_tensor().data_ptr() + 4)
@@ -159,7 +164,7 @@ class CudaKernels:
             self.launches += 1
             _check(self._core.sb_skinny_linear(_p(a), _p(w), _p(out), m, n, k, _DT[out.dtype], 0, _stream()), "skinny linear")
             return
-        if (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self.use_tcgen05 and m >= self.TCGEN05_MIN_ROWS
+        if (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self._tcgen05_worthwhile(m, n)
                 and self._core.sb_gemm_tcgen05_supports(m, n, k, 0)):
             self.launches += 1
             _check(self._core.sb_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, 0, self._wait_flag(), _stream()), "tcgen05 product")
@@ -177,7 +182,7 @@ class CudaKernels:
             _check(self._core.sb_skinny_linear(_p(h), _p(w_gate_up), _p(out), t, inter, k, _DT[out.dtype], 1, _stream()),
                    "skinny gate/up")
             return
-        if (h.dtype == torch.bfloat16 and self.use_tcgen05 and t >= self.TCGEN05_MIN_ROWS
+        if (h.dtype == torch.bfloat16 and self._tcgen05_worthwhile(t, 2 * inter)
                 and self._core.sb_gemm_tcgen05_supports(t, inter, k, 1)):
             self.launches += 1
             _check(self._core.sb_gemm_tcgen05(_p(h), _p(w_gate_up), _p(out), t, inter, k, 1, self._wait_flag(), _stream()),

@@ -405,7 +405,11 @@ def test_tcgen05_product(K, m, n, k):
     out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
     assert K._core.sb_gemm_tcgen05_supports(m, n, k, 0) == 1
     before = K.launches
-    K.linear(a, w, out)
+    K.TCGEN05_MIN_TILES = 1            # small cases too go to the kernel under test
+    try:
+        K.linear(a, w, out)
+    finally:
+        K.TCGEN05_MIN_TILES = type(K).TCGEN05_MIN_TILES
     assert K.launches == before + 1, "these sizes must take the hand-written kernel"
     K.check_errors()
     ref = a.double() @ w.double().T
@@ -421,7 +425,11 @@ def test_tcgen05_product(K, m, n, k):
     torch.testing.assert_close(out.float(), lib.float(), atol=float(ref.abs().max()) * 2.0 ** -7, rtol=0)
     if m > 64:
         part = torch.empty(64, n, device=DEV, dtype=torch.bfloat16)
-        K.linear(a[m - 64:].contiguous(), w, part)
+        K.TCGEN05_MIN_TILES = 1
+        try:
+            K.linear(a[m - 64:].contiguous(), w, part)
+        finally:
+            K.TCGEN05_MIN_TILES = type(K).TCGEN05_MIN_TILES
         assert torch.equal(part, out[m - 64:])
 
 
@@ -431,7 +439,13 @@ def test_tcgen05_gate_up_with_swiglu(K, m, inter, k):
     w = (torch.randn(2 * inter, k, device=DEV) * 0.05).to(torch.bfloat16)
     fused = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
     assert K._core.sb_gemm_tcgen05_supports(m, inter, k, 1) == 1
-    K.gate_up_swiglu(h, w, fused)
+    before = K.launches
+    K.TCGEN05_MIN_TILES = 1
+    try:
+        K.gate_up_swiglu(h, w, fused)
+    finally:
+        K.TCGEN05_MIN_TILES = type(K).TCGEN05_MIN_TILES
+    assert K.launches == before + 1
     K.check_errors()
     ref = torch.empty_like(fused)
     E.gate_up_swiglu(h, w, ref)
