@@ -9,13 +9,17 @@
 using namespace sb;
 
 // ---------------------------------------------------------------- embedding
+// A token id below zero, -(s+1), stands for "the token last sampled for state slot s": it is read from
+// last_token[s], where the sampling kernel left it, so that a decode step can be launched before the host has
+// seen the previous step's tokens.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out,
-                                 int dim, int vocab) {
+                                 int dim, int vocab, const int* __restrict__ last_token, int n_slots) {
   const int t = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
   int tok = tokens[t];
+  if (tok < 0 && last_token != nullptr && -tok - 1 < n_slots) tok = last_token[-tok - 1];
   const bool ok = tok >= 0 && tok < vocab;
   const T* src = table + (size_t)(ok ? tok : 0) * dim;
   float* dst = out + (size_t)t * dim;
@@ -23,15 +27,16 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
 }
 
 SB_EXPORT int sb_embedding(const int* tokens, const void* table, float* out, int n_tokens, int dim, int vocab, int dtype,
-                           cudaStream_t stream) {
+                           const int* last_token, int n_slots, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (dim <= 0 || vocab <= 0) return SB_ERR_SHAPE;
   const int threads = dim >= 1024 ? 256 : 128;
   if (dtype == SB_DTYPE_F32)
-    SB_PDL_CHECK(launch_pdl(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, dim, vocab));
+    SB_PDL_CHECK(launch_pdl(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, dim, vocab,
+                            last_token, n_slots));
   else if (dtype == SB_DTYPE_BF16)
     SB_PDL_CHECK(launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
-                            (const __nv_bfloat16*)table, out, dim, vocab));
+                            (const __nv_bfloat16*)table, out, dim, vocab, last_token, n_slots));
   else
     return SB_ERR_DTYPE;
   return 0;
@@ -388,7 +393,7 @@ __device__ __forceinline__ unsigned long long sample_key(float s, int i) {
 __global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                               const int* __restrict__ req_ids, const int* __restrict__ tok_index, uint32_t seed_lo,
                               uint32_t seed_hi, int vocab, int* __restrict__ out, unsigned long long* __restrict__ keys,
-                              int* __restrict__ counters) {
+                              int* __restrict__ counters, const int* __restrict__ slots, int* __restrict__ last_token) {
   __shared__ unsigned long long skey[32];
   const int r = blockIdx.x;
   const float* lr = logits + (size_t)r * vocab;
@@ -433,7 +438,9 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
       if (atomicAdd(counters + r, 1) == (int)gridDim.y - 1) {
         __threadfence();
         const unsigned long long k = atomicExch(keys + r, 0ull);
-        out[r] = k ? (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull)) : 0;
+        const int chosen = k ? (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull)) : 0;
+        out[r] = chosen;
+        if (slots != nullptr && last_token != nullptr) last_token[slots[r]] = chosen;   // for the next step's embedding
         counters[r] = 0;
       }
     }
@@ -442,8 +449,10 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
 
 // work: n_rows 64-bit keys followed by n_rows int counters (16-byte aligned), all zero before the first call;
 // every call leaves them zero.
+// slots / last_token (both or neither): the chosen token of row r is also left in last_token[slots[r]].
 SB_EXPORT int sb_sample(const float* logits, const float* temperature, const int* req_ids, const int* tok_index,
-                        unsigned long long seed, int n_rows, int vocab, int* out, void* work, cudaStream_t stream) {
+                        unsigned long long seed, int n_rows, int vocab, int* out, void* work, const int* slots, int* last_token,
+                        cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab <= 0 || !work) return SB_ERR_SHAPE;
   if (n_rows > 65535) return SB_ERR_LIMIT;
@@ -453,6 +462,6 @@ SB_EXPORT int sb_sample(const float* logits, const float* temperature, const int
   unsigned long long* keys = (unsigned long long*)work;
   int* counters = (int*)(keys + n_rows);
   SB_PDL_CHECK(launch_pdl(sample_kernel, dim3(n_rows, chunks), dim3(threads), 0, stream, logits, temperature, req_ids, tok_index,
-                          (uint32_t)(seed & 0xffffffffULL), (uint32_t)(seed >> 32), vocab, out, keys, counters));
+                          (uint32_t)(seed & 0xffffffffULL), (uint32_t)(seed >> 32), vocab, out, keys, counters, slots, last_token));
   return 0;
 }

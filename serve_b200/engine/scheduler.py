@@ -25,6 +25,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence
 
+from .step import FROM_DEVICE
+
 
 @dataclass
 class SchedRequest:
@@ -33,7 +35,7 @@ class SchedRequest:
     max_new_tokens: int
     temperature: float = 0.0
     stop_ids: Sequence[int] = ()
-    generated: List[int] = field(default_factory=list)
+    generated: List[Optional[int]] = field(default_factory=list)   # None: sampled on the device, not yet read back
     fed: int = 0                 # tokens of prompt+generated already in the cache
     finished: bool = False
     finish_reason: Optional[str] = None
@@ -45,9 +47,12 @@ class SchedRequest:
         return len(self.prompt) + len(self.generated)
 
     def pending(self) -> List[int]:
+        """Tokens not yet in the cache; a token the host has not read back yet stands as FROM_DEVICE."""
         if self.fed >= len(self.prompt):
-            return self.generated[self.fed - len(self.prompt):]
-        return self.prompt[self.fed:] + self.generated
+            rest = self.generated[self.fed - len(self.prompt):]
+        else:
+            rest = self.prompt[self.fed:] + self.generated
+        return [FROM_DEVICE if t is None else t for t in rest]
 
 
 @dataclass
@@ -195,8 +200,9 @@ class Scheduler:
 
     # ---- after the step -----------------------------------------------------
     def update(self, entries: Sequence[PlannedEntry], sampled: Sequence[int]) -> List[SchedRequest]:
-        """Account a finished step. ``sampled``: one token for each entry with ``samples`` set, in order.
-        Returns the requests that finished (the caller gives back their cache)."""
+        """Account a launched step. ``sampled``: one token for each entry with ``samples`` set, in order; None for a
+        token that is still on the device (``resolve`` fills it in later; stopping by a stop id is then found
+        there). Returns the requests that finished (the caller gives back their cache)."""
         self.stats.steps += 1
         done: List[SchedRequest] = []
         it = iter(sampled)
@@ -209,11 +215,12 @@ class Scheduler:
             r.fed += len(e.tokens)
             if not e.samples:
                 continue
-            tok = int(next(it))
+            tok = next(it)
+            tok = int(tok) if tok is not None else None
             r.generated.append(tok)
             if len(r.generated) >= r.max_new_tokens:
                 r.finished, r.finish_reason = True, "length"
-            elif tok in r.stop_ids:
+            elif tok is not None and tok in r.stop_ids:
                 r.finished, r.finish_reason = True, "stop"
             if r.finished:
                 done.append(r)
@@ -223,3 +230,25 @@ class Scheduler:
             if self.reserve_full:
                 self.promised_pages -= self._pages(len(r.prompt) + r.max_new_tokens - 1)
         return done
+
+    def resolve(self, request: SchedRequest, index: int, token: int) -> bool:
+        """The token generated at ``index`` has reached the host. Returns True if it ends the request (a stop id):
+        the request leaves the queues, what was generated past it (a step launched meanwhile) is dropped, and the
+        caller gives back its cache."""
+        if index >= len(request.generated):
+            return False                      # the request was cut short by an earlier stop id
+        request.generated[index] = int(token)
+        if int(token) in request.stop_ids and (not request.finished or index < len(request.generated) - 1):
+            del request.generated[index + 1:]
+            newly = not request.finished
+            request.finished, request.finish_reason = True, "stop"
+            if request in self.running:
+                self.running.remove(request)
+                if self.reserve_full:
+                    self.promised_pages -= self._pages(len(request.prompt) + request.max_new_tokens - 1)
+            if request in self.waiting:
+                self.waiting.remove(request)
+            if newly:
+                self.finished.append(request)
+            return True
+        return False

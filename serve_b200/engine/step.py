@@ -18,6 +18,10 @@ import numpy as np
 import torch
 
 
+# In place of a token id: "the token that was last sampled for this request" (it is still on the device).
+FROM_DEVICE = -1
+
+
 @dataclass
 class StepEntry:
     rid: Hashable
@@ -50,6 +54,7 @@ class StepContext:
     logit_rows: torch.Tensor    # [L] int32 indices into the T tokens
     block_tables: List[torch.Tensor]   # per cache group: [R, W] int32
     rids: List[Hashable] = field(default_factory=list)
+    last_token: Optional[torch.Tensor] = None   # [max_slots] int32: the token last sampled for each state slot
 
 
 def _align4(n: int) -> int:
@@ -89,7 +94,10 @@ class Stepper:
         self._dev: Optional[torch.Tensor] = None
         self._graphs: Dict[tuple, object] = {}
         self.launched_graphs = 0
+        # the token last sampled for each state slot (written by the sampling kernel, read by the embedding)
+        self.last_token = torch.zeros(cache.max_slots, dtype=torch.int32, device=runtime.device)
         self.last_h2d_bytes = 0
+        self.last_slots = None      # device view of the state slots of the last step's rows
 
     # ---- buffers ----------------------------------------------------------
     def _buffers(self, n: int):
@@ -188,10 +196,13 @@ class Stepper:
             row_of = np.repeat(np.arange(r, dtype=np.int64), ql)
             pos = np.arange(t, dtype=np.int64) - cu[:-1][row_of] + np.asarray(starts, dtype=np.int64)[row_of]
         vocab = self.model.spec.vocab_size
-        if toks.min() < 0 or toks.max() >= vocab:
-            bad = int(toks[(toks < 0) | (toks >= vocab)][0])
+        if toks.min() < 0:
+            # FROM_DEVICE becomes -(slot + 1): the embedding kernel then reads the slot's last sampled token
+            slot_of = np.asarray([self.cache.slot(rid) for rid in rids], dtype=np.int64)[row_of]
+            toks = np.where(toks == FROM_DEVICE, -(slot_of + 1), np.where(toks < 0, vocab, toks))
+        if toks.max() >= vocab:
             self._undo_plan(batch)
-            raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
+            raise ValueError(f"a token id is outside the vocabulary of {vocab}")
         h[o: o + t] = toks
         h[pos_o: pos_o + t] = pos
         h[row_o: row_o + t] = row_of
@@ -221,8 +232,9 @@ class Stepper:
             tokens=view("tokens"), positions=view("positions"), token_row=view("token_row"),
             cu_q=view("cu_q"), kv_len=view("kv_len"), slots=view("slots"), logit_rows=view("logit_rows"),
             block_tables=[dev[off: off + rr * w].view(rr, w) for off, rr, w in lay.tables],
-            rids=rids,
+            rids=rids, last_token=self.last_token,
         )
+        self.last_slots = ctx.slots
         if graphable:
             logits = self._run_graph(ctx, r, max(new_lens))
         else:

@@ -140,10 +140,12 @@ class CudaKernels:
                 raise KernelError(f"{n} cache writes met a missing page or a block index beyond the block table")
 
     # ---- kernels ----------------------------------------------------------
-    def embedding(self, tokens, table, out) -> None:
+    def embedding(self, tokens, table, out, last_token=None) -> None:
+        """out[t] = table[tokens[t]]; an id -(s+1) is replaced by last_token[s] (the token last sampled for slot s)."""
         self.launches += 1
         _check(self._core.sb_embedding(_p(tokens), _p(table), _p(out), tokens.shape[0], table.shape[1], table.shape[0],
-                                       _DT[table.dtype], _stream()), "embedding")
+                                       _DT[table.dtype], _p(last_token), last_token.shape[0] if last_token is not None else 0,
+                                       _stream()), "embedding")
 
     def add_rmsnorm(self, x, delta, weight, eps, out) -> None:
         self.launches += 1
@@ -259,7 +261,7 @@ class CudaKernels:
             self._tickets.append(torch.zeros(max(n, 4096), dtype=torch.int32, device=self.device))
         return self._tickets[-1]
 
-    def sample(self, logits, temperature, req_ids, tok_index, seed, out) -> None:
+    def sample(self, logits, temperature, req_ids, tok_index, seed, out, slots=None, last_token=None) -> None:
         self.launches += 1
         n = logits.shape[0]
         if self._sample_work is None or self._sample_work.numel() < 3 * n:
@@ -267,7 +269,8 @@ class CudaKernels:
             self._sample_work = torch.zeros(3 * max(n, 256), dtype=torch.int32, device=self.device)
             self._keep.append(self._sample_work)
         _check(self._core.sb_sample(_p(logits), _p(temperature), _p(req_ids), _p(tok_index), ctypes.c_ulonglong(seed),
-                                    n, logits.shape[1], _p(out), _p(self._sample_work), _stream()), "sample")
+                                    n, logits.shape[1], _p(out), _p(self._sample_work), _p(slots), _p(last_token), _stream()),
+               "sample")
 
 
 _INSTANCES: Dict[str, CudaKernels] = {}

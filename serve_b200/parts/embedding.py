@@ -31,7 +31,7 @@ class TokenEmbedding(Part):
 
     def forward(self, tokens, ctx):
         x = torch.empty((tokens.shape[0], self.hidden), dtype=torch.float32, device=self.rt.device)
-        self.rt.kernels.embedding(tokens, self.table, x)
+        self.rt.kernels.embedding(tokens, self.table, x, getattr(ctx, "last_token", None))
         return x
 
 

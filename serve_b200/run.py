@@ -77,31 +77,89 @@ def generate(model: Engine, requests: Sequence[Request], temperature: float = 0.
         ids = r.input_ids.tolist() if isinstance(r.input_ids, torch.Tensor) else list(r.input_ids)
         sched.add(SchedRequest(i, ids[: r.input_length], r.max_new_tokens, temperature, stop))
     model.last_stats = sched.stats
-    while sched.has_work():
-        planned = sched.plan()
-        for victim in sched.evicted:
-            model.end(victim.rid)
-        if not planned:
-            raise RuntimeError("the scheduler found nothing to run although requests are waiting")
-        entries = [StepEntry(p.request.rid, p.tokens, [len(p.tokens) - 1] if p.samples else []) for p in planned]
-        logits = model.step(entries)
-        sampling = [p.request for p in planned if p.samples]
-        tokens: List[int] = []
-        if sampling:
-            out = sampler.sample(logits, [r.temperature for r in sampling], [r.rid for r in sampling],
-                                 [len(r.generated) for r in sampling])
-            tokens = out.tolist()   # device -> host: the step's result
-        done = sched.update(planned, tokens)
+    # Steps are launched one ahead of the host's knowledge of their tokens: step N+1 takes the tokens step N sampled
+    # straight from the device (FROM_DEVICE), and the host reads step N's tokens while step N+1 runs. A stop id is
+    # therefore found one step late (that step's work for the request is dropped). With return_logits and a stop id
+    # the logits of the last step must still be there when the stop is found, so that case runs step by step.
+    pipelined = not (return_logits and stop)
+    on_cuda = model.rt.device.type == "cuda"
+    staging = [None, None]
+    turn = 0
+    inflight = None          # (requests, indices of their new tokens, host tensor, event, step record)
+    ended = set()
+
+    def end(r):
+        if r.rid not in ended:
+            ended.add(r.rid)
+            model.end(r.rid)
+
+    def resolve(rec):
+        reqs, idxs, host, event, stamp, step_logits = rec
+        if event is not None:
+            event.synchronize()
+        toks = host[: len(reqs)].tolist()        # device -> host: the step's result
+        for row, (r, i, tok) in enumerate(zip(reqs, idxs, toks)):
+            if sched.resolve(r, i, tok):
+                if return_logits and step_logits is not None:
+                    r.last_logits = step_logits[row].clone()
+                end(r)
         if timeline is not None:
-            n_dec = sum(1 for p in planned if len(p.tokens) == 1 and p.samples and p.request.generated and len(p.request.generated) > 1)
-            timeline.append((time.perf_counter(), sum(len(p.tokens) for p in planned) - n_dec, n_dec,
-                             model.stepper.last_h2d_bytes + 12 * len(sampling)))
-        if done:
-            rows = {id(r): i for i, r in enumerate(sampling)}
-            for r in done:
-                if return_logits:
-                    r.last_logits = logits[rows[id(r)]].clone()
-                model.end(r.rid)
+            timeline.append((time.perf_counter(),) + stamp)
+
+    while sched.has_work() or inflight is not None:
+        launched = None
+        if sched.has_work():
+            planned = sched.plan()
+            if sched.evicted and inflight is not None:
+                resolve(inflight)                # an evicted request is recomputed from tokens the host must know
+                inflight = None
+                if not sched.has_work():
+                    continue
+                planned = [p for p in planned if not p.request.finished]
+            for victim in sched.evicted:
+                if not victim.finished:
+                    model.end(victim.rid)
+            if not planned:
+                if inflight is not None:
+                    resolve(inflight)
+                    inflight = None
+                    continue
+                raise RuntimeError("the scheduler found nothing to run although requests are waiting")
+            entries = [StepEntry(p.request.rid, p.tokens, [len(p.tokens) - 1] if p.samples else []) for p in planned]
+            logits = model.step(entries)
+            sampling = [p.request for p in planned if p.samples]
+            host = event = None
+            if sampling:
+                out = sampler.sample(logits, [r.temperature for r in sampling], [r.rid for r in sampling],
+                                     [len(r.generated) for r in sampling], [model.cache.slot(r.rid) for r in sampling],
+                                     model.stepper.last_token)
+                turn ^= 1
+                if staging[turn] is None or staging[turn].numel() < len(sampling):
+                    staging[turn] = torch.empty(max(64, len(sampling)), dtype=torch.int32, pin_memory=on_cuda)
+                host = staging[turn]
+                host[: len(sampling)].copy_(out, non_blocking=True)
+                if on_cuda:
+                    event = torch.cuda.Event()
+                    event.record()
+            n_dec = sum(1 for p in planned if len(p.tokens) == 1 and p.samples and p.request.generated)
+            stamp = (sum(len(p.tokens) for p in planned) - n_dec, n_dec, model.stepper.last_h2d_bytes + 16 * len(sampling))
+            idxs = [len(r.generated) for r in sampling]
+            done = sched.update(planned, [None] * len(sampling))
+            if done:
+                rows = {id(r): i for i, r in enumerate(sampling)}
+                for r in done:
+                    if return_logits:
+                        r.last_logits = logits[rows[id(r)]].clone()
+                    end(r)
+            launched = (sampling, idxs, host, event, stamp, logits if (return_logits and not pipelined) else None)
+        if inflight is not None:
+            resolve(inflight)                    # the previous step's tokens, read while this step runs
+        inflight = launched if (launched is not None and launched[0]) else None
+        if launched is not None and not launched[0] and timeline is not None:
+            timeline.append((time.perf_counter(),) + launched[4])
+        if inflight is not None and not pipelined:
+            resolve(inflight)
+            inflight = None
     by_id = {r.rid: r for r in sched.finished}
     out_requests = []
     for i, r in enumerate(requests):

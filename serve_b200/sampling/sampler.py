@@ -26,8 +26,11 @@ class Sampler:
         self._event = None
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], request_ids: Sequence[int],
-               token_indices: Sequence[int]) -> torch.Tensor:
-        """logits [L, V] float32 -> int32 [L] on the device (one token per row)."""
+               token_indices: Sequence[int], slots: Sequence[int] = None, last_token: torch.Tensor = None) -> torch.Tensor:
+        """logits [L, V] float32 -> int32 [L] on the device (one token per row).
+
+        With ``slots`` and ``last_token`` the token of row r is also left in last_token[slots[r]] on the device, where
+        the next step's embedding finds it (FROM_DEVICE) without a trip through the host."""
         n = logits.shape[0]
         if not (len(temperatures) == len(request_ids) == len(token_indices) == n):
             raise ValueError("one temperature, request id and token index per row of logits is needed")
@@ -35,19 +38,23 @@ class Sampler:
             raise ValueError("temperature must not be negative")
         if self._host is None or self._host.shape[1] < n:
             cap = max(64, 1 << (n - 1).bit_length())
-            self._host = torch.empty((3, cap), dtype=torch.int32, pin_memory=self._pin)
-            self._dev = torch.empty((3, cap), dtype=torch.int32, device=self.device)
+            self._host = torch.empty((4, cap), dtype=torch.int32, pin_memory=self._pin)
+            self._dev = torch.empty((4, cap), dtype=torch.int32, device=self.device)
         if self._event is not None:
             self._event.synchronize()       # the copy that last used the staging buffer has finished
         h = self._host.numpy()
         h[0, :n].view("float32")[:] = temperatures
         h[1, :n] = request_ids
         h[2, :n] = token_indices
+        feed_back = slots is not None and last_token is not None
+        if feed_back:
+            h[3, :n] = slots
         self._dev.copy_(self._host, non_blocking=True)
         if self._pin:
             if self._event is None:
                 self._event = torch.cuda.Event()
             self._event.record()
         out = torch.empty(n, dtype=torch.int32, device=self.device)
-        self.kernels.sample(logits, self._dev[0, :n].view(torch.float32), self._dev[1, :n], self._dev[2, :n], self.seed, out)
+        self.kernels.sample(logits, self._dev[0, :n].view(torch.float32), self._dev[1, :n], self._dev[2, :n], self.seed, out,
+                            self._dev[3, :n] if feed_back else None, last_token if feed_back else None)
         return out

