@@ -36,12 +36,28 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// What the q/k/v product of an attention layer does with its columns instead of storing them all (ROPE):
+// columns are [q heads | k heads | v heads] x head_dim; q and k are rotated in adjacent pairs (2j, 2j+1) by
+// position * inv_freq[j] (serve/model.py:234-244), q goes to ``out``, rotated k and plain v go straight into
+// the request's cache page (serve/model.py:120-124), as the separate rotary kernel does.
+struct RopeArgs {
+  const int* positions;
+  const int* token_row;
+  const float* inv_freq;
+  int rot, H, Hkv, D;
+  bf16* kc;
+  bf16* vc;
+  const int* block_table;
+  int bt_width, ps, num_pages, write_cache;
+  int* errors;
+};
+
 // MT: tiles of 16 activation rows (M <= 16*MT); HALF: only rows 0..7 of the single tile exist (M <= 8).
 // NT: tiles of 8 output columns per block (2 for very wide outputs: fewer, fatter blocks).
 // GU: fused gate/up with SwiGLU epilogue. OutT: bf16 or float.
-template <int MT, bool HALF, int NT, bool GU, typename OutT>
+template <int MT, bool HALF, int NT, bool GU, bool ROPE, typename OutT>
 __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w,
-                                                                OutT* __restrict__ out, int M, int N, int K) {
+                                                                OutT* __restrict__ out, int M, int N, int K, const RopeArgs ra) {
   constexpr int NW = GU ? 2 : 1;
   constexpr int NB = NW * NT;                        // 8-column tiles of w rows a lane streams
   constexpr int BN = 8 * NT;                         // output columns per block
@@ -161,27 +177,58 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
       const float gte = to_float(__float2bfloat16_rn(s0)), up = to_float(__float2bfloat16_rn(s1));
       v = gte / (1.0f + expf(-gte)) * up;
     }
+    if (ROPE) {
+      const int head = n / ra.D, i = n - head * ra.D;
+      v = to_float(__float2bfloat16_rn(v));            // as the unfused path stores q/k/v before rotating
+      const int pos = ra.positions[m];
+      if (head < ra.H + ra.Hkv && i < ra.rot) {
+        // the partner of the pair sits in the neighbouring column of the same tile
+        float sp = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < WARPS; ++wv) sp += red[wv][vt][t][ml * 8 + (nn ^ 1)];
+        sp = to_float(__float2bfloat16_rn(sp));
+        float sn, cs;
+        sincosf((float)pos * ra.inv_freq[i >> 1], &sn, &cs);
+        v = (i & 1) ? (v * cs + sp * sn) : (v * cs - sp * sn);
+      }
+      if (head < ra.H) {
+        out[(size_t)m * N + n] = from_float<OutT>(v);
+      } else if (ra.write_cache) {
+        const int blk = pos / ra.ps;
+        const int page = (blk < ra.bt_width && pos >= 0) ? ra.block_table[(size_t)ra.token_row[m] * ra.bt_width + blk] : -1;
+        if (page >= 0 && page < ra.num_pages) {
+          const bool is_k = head < ra.H + ra.Hkv;
+          const int kvh = is_k ? head - ra.H : head - ra.H - ra.Hkv;
+          bf16* dst = (is_k ? ra.kc : ra.vc) + (((size_t)page * ra.Hkv + kvh) * ra.ps + (pos - blk * ra.ps)) * ra.D + i;
+          *dst = __float2bfloat16_rn(v);
+        } else if (n == (ra.H * ra.D)) {
+          atomicAdd(ra.errors, 1);
+        }
+      }
+      continue;
+    }
     out[(size_t)m * N + n] = from_float<OutT>(v);
   }
 }
 
-template <int MT, bool HALF, int NT, bool GU, typename OutT>
-int launch(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
-  SB_PDL_CHECK(launch_pdl(skinny_linear_kernel<MT, HALF, NT, GU, OutT>, dim3((N + 8 * NT - 1) / (8 * NT)), dim3(THREADS), 0, stream,
-                          (const bf16*)a, (const bf16*)w, (OutT*)out, M, N, K));
+template <int MT, bool HALF, int NT, bool GU, bool ROPE, typename OutT>
+int launch(const void* a, const void* w, void* out, int M, int N, int K, const RopeArgs& ra, cudaStream_t stream) {
+  SB_PDL_CHECK(launch_pdl(skinny_linear_kernel<MT, HALF, NT, GU, ROPE, OutT>, dim3((N + 8 * NT - 1) / (8 * NT)), dim3(THREADS), 0,
+                          stream, (const bf16*)a, (const bf16*)w, (OutT*)out, M, N, K, ra));
   return 0;
 }
 
 template <bool GU, typename OutT>
 int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
+  const RopeArgs none = {};
   // more than ~8 blocks of 8 columns per SM: halve the block count, double the bytes each keeps in flight
   const bool wide = !GU && N >= 148 * 8 * 8;
   if (M <= 8) {
-    if (wide) return launch<1, true, 2, GU, OutT>(a, w, out, M, N, K, stream);
-    return launch<1, true, 1, GU, OutT>(a, w, out, M, N, K, stream);
+    if (wide) return launch<1, true, 2, GU, false, OutT>(a, w, out, M, N, K, none, stream);
+    return launch<1, true, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
   }
-  if (M <= 16 || GU) return launch<1, false, 1, GU, OutT>(a, w, out, M, N, K, stream);
-  return launch<2, false, 1, GU, OutT>(a, w, out, M, N, K, stream);
+  if (M <= 16 || GU) return launch<1, false, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
+  return launch<2, false, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
 }
 
 }  // namespace
@@ -204,4 +251,23 @@ SB_EXPORT int sb_skinny_linear(const void* a, const void* w, void* out, int M, i
   if (out_dtype == SB_DTYPE_BF16) return launch_mt<false, bf16>(a, w, out, M, N, K, stream);
   if (out_dtype == SB_DTYPE_F32) return launch_mt<false, float>(a, w, out, M, N, K, stream);
   return SB_ERR_DTYPE;
+}
+
+// The q/k/v product of an attention layer with rotation and cache write in its epilogue (see RopeArgs):
+// a [M,K], w [(H + 2 Hkv) * D, K]; out [M, (H + 2 Hkv) * D] receives the rotated queries (its k and v columns are
+// left as they were); rotated keys and values go to kc, vc [num_pages, Hkv, ps, D]. Pairs are adjacent columns.
+SB_EXPORT int sb_skinny_qkv_rope(const void* a, const void* w, void* out, int M, int K, const int* positions, const int* token_row,
+                                 const float* inv_freq, int rot, int H, int Hkv, int D, void* kc, void* vc, const int* block_table,
+                                 int bt_width, int ps, int num_pages, int write_cache, int* errors, cudaStream_t stream) {
+  const int N = (H + 2 * Hkv) * D;
+  if (!sb_skinny_linear_supports(M, N, K, 0)) return SB_ERR_SHAPE;
+  if (H <= 0 || Hkv <= 0 || D <= 0 || (D % 8) || rot < 0 || rot > D || (rot & 1) || ps <= 0) return SB_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(w)) return SB_ERR_ALIGN;
+  RopeArgs ra;
+  ra.positions = positions; ra.token_row = token_row; ra.inv_freq = inv_freq; ra.rot = rot; ra.H = H; ra.Hkv = Hkv; ra.D = D;
+  ra.kc = (bf16*)kc; ra.vc = (bf16*)vc; ra.block_table = block_table; ra.bt_width = bt_width; ra.ps = ps; ra.num_pages = num_pages;
+  ra.write_cache = write_cache; ra.errors = errors;
+  if (M <= 8) return launch<1, true, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+  if (M <= 16) return launch<1, false, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+  return launch<2, false, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
 }

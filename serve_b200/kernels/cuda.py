@@ -85,6 +85,7 @@ class CudaKernels:
         self.force_simt_attention = False   # tests: run bfloat16 through the plain-arithmetic kernel
         self.use_skinny_linear = True       # tests: False sends every product to the library
         self.use_tcgen05 = True             # tests: False keeps many-row products in the library
+        self.fuse_rope = True               # tests: False runs the rotary kernel after the q/k/v product
         self._sample_work = None
         self._keep = []
         self._tickets = []                   # zeroed int32 buffers of the split-key merge (kept alive for graphs)
@@ -206,6 +207,27 @@ class CudaKernels:
             _p(qkv), _p(positions), _p(token_row), _p(inv_freq), pairing, rotary_dim, heads, kv_heads, head_dim,
             _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], page_size, num_pages,
             1 if write_cache else 0, _p(self.errors_tensor()), qkv.shape[0], _DT[qkv.dtype], _stream()), "rope_cache_write")
+
+    def qkv_rope_cache(self, h, w_qkv, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
+                       k_cache, v_cache, block_table, page_size, write_cache) -> None:
+        """qkv = h @ w_qkv^T, queries and keys rotated, keys and values written to the cache pages.
+
+        For a handful of rows, bfloat16 and adjacent rotary pairs this is one kernel (the product with rotation and
+        cache write in its epilogue; only the query columns of ``qkv`` are then written). Otherwise the product and
+        the rotary kernel run one after the other."""
+        m, k = h.shape
+        n = qkv.shape[1]
+        if (h.dtype == torch.bfloat16 and self.use_skinny_linear and self.fuse_rope and pairing == 1 and head_dim % 8 == 0
+                and self._core.sb_skinny_linear_supports(m, n, k, 0)):
+            self.launches += 1
+            _check(self._core.sb_skinny_qkv_rope(
+                _p(h), _p(w_qkv), _p(qkv), m, k, _p(positions), _p(token_row), _p(inv_freq), rotary_dim, heads, kv_heads, head_dim,
+                _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], page_size, k_cache.shape[0],
+                1 if write_cache else 0, _p(self.errors_tensor()), _stream()), "q/k/v product with rotation")
+            return
+        self.linear(h, w_qkv, qkv)
+        self.rope_cache_write(qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
+                              k_cache, v_cache, block_table, page_size, write_cache)
 
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
                   page_size, scale, window, out, shape) -> None:

@@ -16,6 +16,7 @@ import math
 import torch
 
 from .base import CacheNeed, Mixer, TensorDecl, build_part, register_part
+from .rotary import PAIRING_HALF, PAIRING_INTERLEAVED
 
 
 @register_part("mixer", "attention")
@@ -59,8 +60,24 @@ class Attention(Mixer):
     def ignorable_tensors(self):
         return [self.prefix + "rotary_emb.inv_freq"]
 
+    def _adjacent_pairs(self, w: torch.Tensor, n_heads: int) -> torch.Tensor:
+        """Rows of a q or k projection reordered inside every head so that the two elements of a rotary pair
+        (j, j + rot/2) become neighbours (2j, 2j+1). Scores q.k do not notice a reordering of the head's elements
+        that queries and keys share; the rotation can then be done wherever two neighbouring columns meet, e.g. in
+        the epilogue of the product. (The reference stores its weights in this order too,
+        serve/hf_utils/convert_hf_checkpoint.py:115-118.)"""
+        rot, d = self.position.rotary_dim, self.head_dim
+        idx = torch.arange(d)
+        idx[:rot] = torch.stack([torch.arange(rot // 2), torch.arange(rot // 2) + rot // 2], dim=1).reshape(-1)
+        return w.view(n_heads, d, -1)[:, idx.to(w.device)].reshape(n_heads * d, -1)
+
     def load(self, tensors):
-        self.w_qkv = torch.cat([tensors[self.q_name], tensors[self.k_name], tensors[self.v_name]], dim=0).contiguous()
+        wq, wk = tensors[self.q_name], tensors[self.k_name]
+        self.pairing = self.position.pairing
+        if self.position.rotary_dim > 0 and self.position.pairing == PAIRING_HALF:
+            wq, wk = self._adjacent_pairs(wq, self.heads), self._adjacent_pairs(wk, self.kv_heads)
+            self.pairing = PAIRING_INTERLEAVED
+        self.w_qkv = torch.cat([wq, wk, tensors[self.v_name]], dim=0).contiguous()
         self.w_o = tensors[self.o_name].contiguous()
 
     def cache_need(self):
@@ -70,10 +87,9 @@ class Attention(Mixer):
         rt = self.rt
         t = h.shape[0]
         qkv = rt.empty_act((t, self.q_size + 2 * self.kv_size))
-        rt.kernels.linear(h, self.w_qkv, qkv)
         block_table = ctx.block_tables[cache.group]
-        rt.kernels.rope_cache_write(
-            qkv, ctx.positions, ctx.token_row, self.position.inv_freq, self.position.pairing,
+        rt.kernels.qkv_rope_cache(
+            h, self.w_qkv, qkv, ctx.positions, ctx.token_row, self.position.inv_freq, self.pairing,
             self.position.rotary_dim, self.heads, self.kv_heads, self.head_dim,
             cache.k, cache.v, block_table, cache.page_size, cache.writes,
         )

@@ -61,6 +61,12 @@ class EmuKernels:
         self.linear(h, w_gate_up, gate_up)
         self.swiglu(gate_up, out)
 
+    def qkv_rope_cache(self, h, w_qkv, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
+                       k_cache, v_cache, block_table, page_size, write_cache):
+        self.linear(h, w_qkv, qkv)
+        self.rope_cache_write(qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
+                              k_cache, v_cache, block_table, page_size, write_cache)
+
     def rope_cache_write(self, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
                          k_cache, v_cache, block_table, page_size, write_cache):
         t = qkv.shape[0]

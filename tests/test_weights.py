@@ -50,7 +50,10 @@ def test_random_folder_loads_and_is_seeded(tmp_path):
     load_weights(m, str(tmp_path / "m1"), torch.float32, "cpu")
     att = m.blocks[2].mixer
     assert att.w_qkv.shape == ((6 + 2 * 3) * 32, 192) and att.w_qkv.dtype == torch.float32
-    assert torch.equal(att.w_qkv[6 * 32: 9 * 32], w1["model.layers.2.self_attn.k_proj.weight"])
+    # fused rows: q heads, k heads, v heads; inside a q or k head the two elements of a rotary pair are neighbours
+    wk = w1["model.layers.2.self_attn.k_proj.weight"]
+    assert torch.equal(att.w_qkv[6 * 32: 6 * 32 + 32: 2], wk[:16]) and torch.equal(att.w_qkv[6 * 32 + 1: 6 * 32 + 32: 2], wk[16:32])
+    assert torch.equal(att.w_qkv[9 * 32:], w1["model.layers.2.self_attn.v_proj.weight"])
     assert m.blocks[0].feed_forward.w_gate_up.shape == (640, 192)
 
 
