@@ -1,0 +1,439 @@
+// Paged causal attention for prompt portions on the fifth-generation tensor cores (head_dim 64, bfloat16).
+//
+// Work is cut as in attention_mma.cu: per (request, kv head), with the G = H / Hkv query heads that share the kv
+// head folded into the row dimension: row m stands for (token m / G, head hk*G + m % G). A CTA owns 128 such
+// rows (128 / G tokens) and walks over the request's keys in tiles of 128:
+//   warp 0     one thread feeds shared memory with TMA: the query tile once (a 4-d box over the q/k/v buffer),
+//              then per tile the key and value pages named by the block table (4-d boxes over the caches,
+//              128-byte swizzle), two stages;
+//   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 x 128 x 64) into tensor memory, and, once the
+//              probabilities of a tile are in shared memory, O_tile = P V (128 x 64 x 128, V read MN-major);
+//              tcgen05.commit signals the readers and frees the stages; S and O_tile are double-buffered so
+//              that the products of one tile run while the softmax of its neighbour does;
+//   warps 2..5 one thread per row: reads its row of S from tensor memory (tcgen05.ld), scale, causal mask on
+//              the diagonal tiles, running maximum and sum, exp2, writes the probabilities as bfloat16 into the
+//              swizzled layout the second product reads, and adds the finished O_tile of the tile before into
+//              its float accumulator in registers (rescaled when the maximum moved). At the end it divides
+//              by the sum and stores 128 bytes of its output row.
+// The recurrences are those of serve/kernels/attn_prefill.py:58-72 with exp2 and a folded log2(e)
+// (attn_prefill.py:330-331); probabilities are rounded to bfloat16 before the second product (attn_prefill.py:71).
+// Every wait is bounded; a wait that runs out raises *error and the CTA still frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#if SB_HEAD_DIM == 64
+
+using namespace sb;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int D = 64;
+constexpr int BM = 128;              // rows per CTA
+constexpr int BN = 128;              // keys per tile
+constexpr int NS = 2;                // key/value stages
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;  // S0, S1 (128 columns each), O0, O1 (64 each); a power of two is asked for
+constexpr unsigned WAIT_LIMIT = 1u << 26;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int Q_BYTES = BM * D * 2, KV_BYTES = BN * D * 2, P_BYTES = BM * BN * 2;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * NS * KV_BYTES + 2 * P_BYTES + 1024;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 32 lanes x 32 columns: thread i of the warp gets lane (base + i), 32 consecutive columns. No wait: several loads
+// may be in flight; tc_wait_ld() before the registers are read.
+__device__ __forceinline__ void tc_load32(uint32_t taddr, float* r) {
+  uint32_t* u = reinterpret_cast<uint32_t*>(r);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]),
+        "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]),
+        "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]),
+        "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart; ``lbo`` is the distance between
+// 64-element swizzle atoms along the non-k dimension of an MN-major operand (not used by K-major operands).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// kind::f16 instruction descriptor: float accumulator, bfloat16 operands; b_mn_major: the second operand has its
+// non-k dimension contiguous in shared memory (values: rows are keys, head elements contiguous)
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct TcParams {
+  const int* block_table; int bt_width;
+  const int* cu_q; const int* kv_len;
+  int H, Hkv, G, ps;
+  float scale_log2;
+  bf16* out;
+  int* error;
+};
+
+__global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                               const __grid_constant__ CUtensorMap map_k,
+                                                               const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+  const int r = blockIdx.z, hk = blockIdx.y;
+  const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
+  const int G = p.G;
+  const int M = qn * G;
+  if (M <= 16) return;                                  // the deep shape takes this request
+  const int tok_per_tile = BM / G;
+  const int n_mtiles = (qn + tok_per_tile - 1) / tok_per_tile;
+  if ((int)blockIdx.x >= n_mtiles) return;
+  const int tile = n_mtiles - 1 - (int)blockIdx.x;      // later rows see more keys: they go first
+  const int tok0 = tile * tok_per_tile;
+  const int L = p.kv_len[r];
+  const int p0 = L - qn;                                // position of the request's first query
+  const int tok_last = min(tok0 + tok_per_tile, qn) - 1;
+  const int hi = p0 + tok_last + 1;                     // keys [0, hi) are seen by some row of the tile
+  const int n_tiles = (hi + BN - 1) / BN;
+
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t q_full, kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
+  unsigned char* Qs = base;
+  unsigned char* Ks = Qs + Q_BYTES;                     // NS stages
+  unsigned char* Vs = Ks + NS * KV_BYTES;               // NS stages
+  unsigned char* Ps = Vs + NS * KV_BYTES;               // 2 buffers of [2 k-blocks][128 rows][128 bytes]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+#pragma unroll
+    for (int s = 0; s < NS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
+      mbar_init(&p_full[b], 4); mbar_init(&o_full[b], 1); mbar_init(&o_empty[b], 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // queries: box {64 elements, G heads, 1 kv head, tokens of the tile} -> rows (token, head)
+      mbar_expect_tx(&q_full, (unsigned)(tok_per_tile * G * D * 2));
+      tma_load_4d(Qs, &map_q, &q_full, 0, 0, hk, q0 + tok0);
+      const int* bt = p.block_table + (size_t)r * p.bt_width;
+      const int pages_per_tile = BN / p.ps;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % NS;
+        if (!mbar_wait(&kv_empty[s], ((j / NS) & 1) ^ 1)) { failed = true; break; }
+        const int kt = j * BN;
+        int n_pages = 0;
+        for (int i = 0; i < pages_per_tile; ++i)
+          if (kt + i * p.ps < hi && (kt + i * p.ps) / p.ps < p.bt_width) ++n_pages;
+        mbar_expect_tx(&kv_full[s], (unsigned)(n_pages * p.ps * D * 2 * 2));
+        for (int i = 0; i < n_pages; ++i) {
+          const int page = bt[(kt + i * p.ps) / p.ps];
+          tma_load_4d(Ks + (size_t)s * KV_BYTES + (size_t)i * p.ps * D * 2, &map_k, &kv_full[s], 0, 0, hk, page);
+          tma_load_4d(Vs + (size_t)s * KV_BYTES + (size_t)i * p.ps * D * 2, &map_v, &kv_full[s], 0, 0, hk, page);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(BM, BN, false);
+      constexpr uint32_t idesc_o = make_idesc(BM, D, true);
+      const uint64_t dq = make_desc(smem_u32(Qs), 0);
+      auto issue_s = [&](int t) {
+        const uint64_t dk = make_desc(smem_u32(Ks + (size_t)(t % NS) * KV_BYTES), 0);
+        const uint32_t acc = tmem_base + (uint32_t)((t & 1) * BN);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) tc_mma(acc, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk != 0 ? 1u : 0u);
+        tc_commit(&s_full[t & 1]);
+      };
+      do {
+        if (!mbar_wait(&q_full, 0) || !mbar_wait(&kv_full[0], 0)) { failed = true; break; }
+        tc_fence_after();
+        issue_s(0);
+        for (int j = 0; j < n_tiles; ++j) {
+          const int b = j & 1;
+          if (j + 1 < n_tiles) {
+            const int t = j + 1;
+            if (!mbar_wait(&kv_full[t % NS], (t / NS) & 1) || !mbar_wait(&s_empty[t & 1], ((t >> 1) & 1) ^ 1)) { failed = true; break; }
+            tc_fence_after();
+            issue_s(t);
+          }
+          if (!mbar_wait(&p_full[b], (j >> 1) & 1) || !mbar_wait(&o_empty[b], ((j >> 1) & 1) ^ 1)) { failed = true; break; }
+          tc_fence_after();
+          // O_tile = P V: P is K-major in two blocks of 64 keys; V is MN-major, 16 keys = 2048 bytes further per step
+          const uint32_t pa = smem_u32(Ps + (size_t)b * P_BYTES), va = smem_u32(Vs + (size_t)(j % NS) * KV_BYTES);
+          const uint32_t acc = tmem_base + (uint32_t)(2 * BN + b * D);
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            const uint64_t dp = make_desc(pa + (uint32_t)((kk >> 2) * (BM * 128) + (kk & 3) * 32), 0);
+            const uint64_t dv = make_desc(va + (uint32_t)(kk * 2048), BN * 128);
+            tc_mma(acc, dp, dv, idesc_o, kk != 0 ? 1u : 0u);
+          }
+          tc_commit(&o_full[b]);
+          tc_commit(&kv_empty[j % NS]);
+        }
+      } while (false);
+    }
+  } else {
+    const int q = warp & 3;                              // the 32 tensor-memory lanes this warp may touch
+    const int row = q * 32 + lane;
+    const int m = tok0 * G + row;
+    const bool row_ok = row < tok_per_tile * G && m < M;
+    const int tok = row_ok ? m / G : 0, head = row_ok ? hk * G + (m - tok * G) : 0;
+    const int pos = row_ok ? p0 + tok : -1;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha = 1.f;
+    const int first_pos = p0 + tok0;                     // smallest position of the tile's rows
+
+    for (int j = 0; j < n_tiles && !failed; ++j) {
+      const int b = j & 1, kt = j * BN;
+      if (!mbar_wait(&s_full[b], (j >> 1) & 1)) { failed = true; break; }
+      tc_fence_after();
+      const bool masked = kt + BN - 1 > first_pos;       // the tile reaches beyond what the first row may see
+      // the whole row of scores in registers: four loads in flight, one wait
+      float sv[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tc_load32(lane_addr + (uint32_t)(b * BN + c * 32), sv + c * 32);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[b]);           // S of this tile has been read
+      float mx = -INFINITY;
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          sv[i] = (kt + i <= pos) ? sv[i] : -INFINITY;
+          mx = fmaxf(mx, sv[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sv[i]);
+      }
+      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      const float use = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha = ex2(m_run - use);
+      m_run = m_new;
+      // probabilities -> shared memory (bfloat16, the swizzled K-major layout of the second product);
+      // ex2(-inf) = 0 takes care of masked entries
+      float sum = 0.f;
+      unsigned char* prow = Ps + (size_t)b * P_BYTES + (size_t)row * 128;
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {                 // 16-byte pieces of 8 keys
+        uint32_t pk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float e0 = ex2(fmaf(sv[c * 8 + 2 * i], p.scale_log2, -use));
+          const float e1 = ex2(fmaf(sv[c * 8 + 2 * i + 1], p.scale_log2, -use));
+          sum += e0 + e1;
+          pk[i] = pack_bf16(e0, e1);
+        }
+        unsigned char* blk = prow + (size_t)(c >> 3) * (BM * 128);   // 64 keys to a k-block
+        *reinterpret_cast<uint4*>(blk + (((c & 7) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l_run = l_run * alpha + sum;
+      // values of keys beyond the sequence (never written, or another tile's leftovers) must not meet a zero
+      // probability as NaN: the rows of this stage beyond hi are cleared
+      if (kt + BN > hi) {
+        if (!mbar_wait(&kv_full[j % NS], (j / NS) & 1)) { failed = true; break; }
+        unsigned char* vt = Vs + (size_t)(j % NS) * KV_BYTES;
+        const int first = hi - kt;                       // rows [first, 128)
+        for (int idx = (warp - 2) * 32 + lane; idx < (BN - first) * 8; idx += 128)
+          *reinterpret_cast<uint4*>(vt + (size_t)(first + (idx >> 3)) * 128 + ((idx & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these writes are read by the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[b]);
+      // the finished O_tile of the tile before joins the accumulator; both were relative to the old maximum
+      if (j >= 1) {
+        const int pb = (j - 1) & 1;
+        if (!mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1)) { failed = true; break; }
+        tc_fence_after();
+        float v[D];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tc_load32(lane_addr + (uint32_t)(2 * BN + pb * D + c * 32), v + c * 32);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = (o[i] + v[i]) * alpha;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_empty[pb]);
+      }
+    }
+    if (!failed) {
+      const int pb = (n_tiles - 1) & 1;
+      if (!mbar_wait(&o_full[pb], ((n_tiles - 1) >> 1) & 1)) failed = true;
+      tc_fence_after();
+      if (!failed) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint32_t pk[D / 2];
+        float v[D];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tc_load32(lane_addr + (uint32_t)(2 * BN + pb * D + c * 32), v + c * 32);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < D / 2; ++i) pk[i] = pack_bf16((o[2 * i] + v[2 * i]) * inv, (o[2 * i + 1] + v[2 * i + 1]) * inv);
+        if (row_ok) {
+          bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)head * D;
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+        }
+      }
+    }
+  }
+  if (failed) atomicExch(p.error, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int encode4(CUtensorMap* map, const void* basep, const cuuint64_t dims[4], const cuuint64_t strides[3], const cuuint32_t box[4]) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) return -300;
+    g_encode = (EncodeTiledFn)fn;
+  }
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult rc = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(basep), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -301 - (int)rc;
+}
+
+}  // namespace
+
+// 1 if sb_attention_tc takes this geometry (else the caller uses the mma.sync kernel).
+SB_EXPORT int sb_attention_tc_supports(int H, int Hkv, int ps, int window, int q_stride) {
+  if (H <= 0 || Hkv <= 0 || H % Hkv) return 0;
+  const int G = H / Hkv;
+  if (G > 128 || (128 % G)) return 0;                   // a tile holds whole tokens: 128 / G of them
+  if (ps < 8 || ps > 128 || (128 % ps)) return 0;       // pages tile the 128-key stage, in whole swizzle atoms
+  if (window > 0) return 0;
+  if (q_stride % 8) return 0;
+  return 1;
+}
+
+// The wide shape of sb_attention_mma (requests with more than 16 rows) on tcgen05; arguments as there.
+// n_tokens: rows of qkv; num_pages: pages of kc / vc.
+SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const void* kc, const void* vc, const int* block_table,
+                              int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale,
+                              void* out, int n_rows, int max_q, int* error, cudaStream_t stream) {
+  if (n_rows <= 0 || max_q <= 0) return 0;
+  if (!sb_attention_tc_supports(H, Hkv, ps, 0, q_stride)) return SB_ERR_SHAPE;
+  if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
+  if (!aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || !aligned16(out) || !error) return SB_ERR_ALIGN;
+  const int G = H / Hkv;
+  CUtensorMap map_q, map_k, map_v;
+  {
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)G, (cuuint64_t)Hkv, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)G * D * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[4] = {(cuuint32_t)D, (cuuint32_t)G, 1, (cuuint32_t)(BM / G)};
+    int rc = encode4(&map_q, qkv, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, (cuuint64_t)num_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)ps * D * 2, (cuuint64_t)Hkv * ps * D * 2};
+    const cuuint32_t box[4] = {(cuuint32_t)D, (cuuint32_t)ps, 1, 1};
+    int rc = encode4(&map_k, kc, dims, strides, box);
+    if (rc) return rc;
+    rc = encode4(&map_v, vc, dims, strides, box);
+    if (rc) return rc;
+  }
+  TcParams p;
+  p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
+  p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.scale_log2 = scale * LOG2E; p.out = (bf16*)out; p.error = error;
+  const int tok_per_tile = BM / G;
+  const int m_tiles = (max_q + tok_per_tile - 1) / tok_per_tile;
+  auto k = attention_tc_kernel;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  k<<<dim3(m_tiles, Hkv, n_rows), THREADS, SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+#else
+
+SB_EXPORT int sb_attention_tc_supports(int, int, int, int, int) { return 0; }
+
+#endif

@@ -52,7 +52,7 @@ def core_jobs():
 
 
 def attention_job(head_dim: int):
-    return {"name": f"sb_attention_hd{head_dim}", "sources": ["attention_simt.cu", "attention_mma.cu"],
+    return {"name": f"sb_attention_hd{head_dim}", "sources": ["attention_simt.cu", "attention_mma.cu", "attention_tc.cu"],
             "defines": [f"SB_HEAD_DIM={head_dim}"]}
 
 
@@ -86,6 +86,7 @@ class CudaKernels:
         self.use_skinny_linear = True       # tests: False sends every product to the library
         self.use_tcgen05 = True             # tests: False keeps many-row products in the library
         self.fuse_rope = True               # tests: False runs the rotary kernel after the q/k/v product
+        self.use_tcgen05_attention = True   # tests: False keeps prompt portions on the mma.sync kernel
         self._sample_work = None
         self._keep = []
         self._tickets = []                   # zeroed int32 buffers of the split-key merge (kept alive for graphs)
@@ -270,6 +271,16 @@ class CudaKernels:
                 nbytes = lib.sb_attention_mma_scratch_bytes(shape.rows, kv_heads, num_splits)
                 scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
+        if (which & 1) and self.use_tcgen05_attention and lib.sb_attention_tc_supports(heads, kv_heads, page_size, window, qkv.shape[1]):
+            # prompt portions on the tensor-memory path; what is left (decoding rows) goes to the deep shape below
+            self.launches += 1
+            _check(lib.sb_attention_tc(
+                _p(qkv), qkv.shape[1], qkv.shape[0], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q),
+                _p(kv_len), heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), _p(out), shape.rows, shape.max_q,
+                self._wait_flag(), _stream()), "tcgen05 attention")
+            which &= ~1
+            if not which:
+                return
         self.launches += (which & 1) + ((which >> 1) & 1) + ((which >> 2) & 1)
         _check(lib.sb_attention_mma(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),

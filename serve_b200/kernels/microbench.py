@@ -61,6 +61,7 @@ def main(argv=None) -> int:
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--graph", action="store_true")
+    ap.add_argument("--legacy-attention", action="store_true", help="prompt attention on the mma.sync kernel instead of tcgen05")
     ap.add_argument("--library", action="store_true", help="send products to the library (cuBLAS) instead of this engine's kernels")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
@@ -70,6 +71,8 @@ def main(argv=None) -> int:
     K = load_kernels(dev, head_dims=(a.head_dim,))
     if a.library:
         K.use_tcgen05 = K.use_skinny_linear = False
+    if a.legacy_attention:
+        K.use_tcgen05_attention = False
     bf = torch.bfloat16
     if a.kernel in ("linear", "gate_up"):
         rows = 2 * a.n if a.kernel == "gate_up" else a.n
