@@ -2,19 +2,22 @@
 //
 // Work is cut as in attention_mma.cu: per (request, kv head), with the G = H / Hkv query heads that share the kv
 // head folded into the row dimension: row m stands for (token m / G, head hk*G + m % G). A CTA owns 128 such
-// rows (128 / G tokens) and walks over the request's keys in tiles of 128:
+// rows (128 / G tokens) and walks over the request's keys in tiles of 64:
 //   warp 0     one thread feeds shared memory with TMA: the query tile once (a 4-d box over the q/k/v buffer),
 //              then per tile the key and value pages named by the block table (4-d boxes over the caches,
 //              128-byte swizzle), two stages;
-//   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 x 128 x 64) into tensor memory, and, once the
-//              probabilities of a tile are in shared memory, O_tile = P V (128 x 64 x 128, V read MN-major);
-//              tcgen05.commit signals the readers and frees the stages; S and O_tile are double-buffered so
-//              that the products of one tile run while the softmax of its neighbour does;
+//   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 x 64 x 64) into one of two score buffers in tensor
+//              memory, and, once the probabilities of a tile are in shared memory, O += P V (128 x 64 x 64, V read
+//              MN-major) into the output accumulator, which stays in tensor memory for the whole walk;
+//              tcgen05.commit signals the readers and frees stages and buffers;
 //   warps 2..5 one thread per row: reads its row of S from tensor memory (tcgen05.ld), scale, causal mask on
-//              the diagonal tiles, running maximum and sum, exp2, writes the probabilities as bfloat16 into the
-//              swizzled layout the second product reads, and adds the finished O_tile of the tile before into
-//              its float accumulator in registers (rescaled when the maximum moved). At the end it divides
-//              by the sum and stores 128 bytes of its output row.
+//              the diagonal tiles, exp2 against a reference maximum, writes the probabilities as bfloat16 into the
+//              swizzled layout the second product reads (two buffers). The reference maximum only follows the
+//              running maximum when that has moved by more than 8 (a factor 256, harmless in bfloat16 and float);
+//              then, and only then, the accumulator in tensor memory is rescaled (tcgen05.ld / tcgen05.st) after
+//              the products issued so far have finished. So in the steady state nobody waits for the second
+//              product. At the end each thread divides its output row by the row's sum and stores 128 bytes.
+// Two CTAs share an SM (64 KB of shared memory, 256 columns of tensor memory each).
 // The recurrences are those of serve/kernels/attn_prefill.py:58-72 with exp2 and a folded log2(e)
 // (attn_prefill.py:330-331); probabilities are rounded to bfloat16 before the second product (attn_prefill.py:71).
 // Every wait is bounded; a wait that runs out raises *error and the CTA still frees its tensor memory.
@@ -31,14 +34,16 @@ namespace {
 
 constexpr int D = 64;
 constexpr int BM = 128;              // rows per CTA
-constexpr int BN = 128;              // keys per tile
-constexpr int NS = 2;                // key/value stages
+constexpr int BN = 64;               // keys per tile (one 128-byte row of probabilities: one k-block of P)
+constexpr int NS = 3;                // key/value stages
+constexpr int BT_CACHE = 1024;       // block-table entries kept in shared memory
 constexpr int THREADS = 192;
-constexpr uint32_t TMEM_COLS = 512;  // S0, S1 (128 columns each), O0, O1 (64 each); a power of two is asked for
+constexpr uint32_t TMEM_COLS = 256;  // S0, S1 (BN columns each), O (64), rounded up to a power of two; two CTAs share an SM
 constexpr unsigned WAIT_LIMIT = 1u << 26;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int Q_BYTES = BM * D * 2, KV_BYTES = BN * D * 2, P_BYTES = BM * BN * 2;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * NS * KV_BYTES + 2 * P_BYTES + 1024;
+constexpr int TILE_BYTES = Q_BYTES + 2 * NS * KV_BYTES + 2 * P_BYTES;  // 96 KB
+constexpr int SMEM_BYTES = TILE_BYTES + 256 + BT_CACHE * 4;             // + barriers + table entries; two CTAs fit an SM
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
@@ -90,6 +95,19 @@ __device__ __forceinline__ void tc_load32(uint32_t taddr, float* r) {
         "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tc_store32(uint32_t taddr, const float* r) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(r);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]),
+        "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]),
+        "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]),
+        "r"(u[30]), "r"(u[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -126,7 +144,7 @@ struct TcParams {
   int* error;
 };
 
-__global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v, const TcParams p) {
   const int r = blockIdx.z, hk = blockIdx.y;
@@ -145,14 +163,28 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
   const int hi = p0 + tok_last + 1;                     // keys [0, hi) are seen by some row of the tile
   const int n_tiles = (hi + BN - 1) / BN;
 
+  // all shared memory is dynamic, so that the tiles start at the CTA's (1024-byte aligned) window base: the
+  // 128-byte swizzle needs that alignment, and a padded request would not let two CTAs share an SM
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2];
-  __shared__ uint32_t tmem_base_s;
-  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
+  unsigned char* base = smem;
   unsigned char* Qs = base;
   unsigned char* Ks = Qs + Q_BYTES;                     // NS stages
   unsigned char* Vs = Ks + NS * KV_BYTES;               // NS stages
-  unsigned char* Ps = Vs + NS * KV_BYTES;               // 2 buffers of [2 k-blocks][128 rows][128 bytes]
+  unsigned char* Ps = Vs + NS * KV_BYTES;               // 2 buffers of [128 rows][128 bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + TILE_BYTES);
+  uint64_t& q_full = bars[0];
+  uint64_t* kv_full = bars + 1;                         // NS: a stage's keys and values have landed
+  uint64_t* kv_empty = bars + 1 + NS;                   // NS: the products that read the stage have finished
+  uint64_t* s_full = bars + 1 + 2 * NS;                 // 2: a score buffer is complete
+  uint64_t* s_empty = bars + 3 + 2 * NS;                // 2: the softmax threads hold it in registers
+  uint64_t* p_full = bars + 5 + 2 * NS;                 // 2: a buffer of probabilities is written
+  uint64_t* p_empty = bars + 7 + 2 * NS;                // 2: the second product that read it has finished
+  uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + 9 + 2 * NS);
+  int* bt_s = reinterpret_cast<int*>(base + TILE_BYTES + 256);
+  if ((smem_u32(base) & 1023u) != 0) {                  // never seen; refuse rather than compute with a wrong swizzle
+    if (threadIdx.x == 0) atomicExch(p.error, 1);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -161,8 +193,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     for (int s = 0; s < NS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
-      mbar_init(&p_full[b], 4); mbar_init(&o_full[b], 1); mbar_init(&o_empty[b], 4);
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4); mbar_init(&p_full[b], 4); mbar_init(&p_empty[b], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -181,11 +212,18 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
   bool failed = false;
 
   if (warp == 0) {
+    // the table entries of the tile's keys, fetched once by the whole warp instead of one dependent load per page
+    const int* bt = p.block_table + (size_t)r * p.bt_width;
+    const int n_blocks = min((hi + p.ps - 1) / p.ps, p.bt_width);
+    if (n_blocks <= BT_CACHE) {
+      for (int i = lane; i < n_blocks; i += 32) bt_s[i] = bt[i];
+      __syncwarp();
+      bt = bt_s;
+    }
     if (lane == 0) {
       // queries: box {64 elements, G heads, 1 kv head, tokens of the tile} -> rows (token, head)
       mbar_expect_tx(&q_full, (unsigned)(tok_per_tile * G * D * 2));
       tma_load_4d(Qs, &map_q, &q_full, 0, 0, hk, q0 + tok0);
-      const int* bt = p.block_table + (size_t)r * p.bt_width;
       const int pages_per_tile = BN / p.ps;
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % NS;
@@ -221,23 +259,24 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
         for (int j = 0; j < n_tiles; ++j) {
           const int b = j & 1;
           if (j + 1 < n_tiles) {
+            // the next tile's scores, as soon as its keys are there and its score buffer has been read
             const int t = j + 1;
             if (!mbar_wait(&kv_full[t % NS], (t / NS) & 1) || !mbar_wait(&s_empty[t & 1], ((t >> 1) & 1) ^ 1)) { failed = true; break; }
             tc_fence_after();
             issue_s(t);
           }
-          if (!mbar_wait(&p_full[b], (j >> 1) & 1) || !mbar_wait(&o_empty[b], ((j >> 1) & 1) ^ 1)) { failed = true; break; }
+          if (!mbar_wait(&p_full[b], (j >> 1) & 1)) { failed = true; break; }
           tc_fence_after();
-          // O_tile = P V: P is K-major in two blocks of 64 keys; V is MN-major, 16 keys = 2048 bytes further per step
+          // O += P V: P is K-major (one block of 64 keys); V is MN-major, 16 keys = 2048 bytes further per step
           const uint32_t pa = smem_u32(Ps + (size_t)b * P_BYTES), va = smem_u32(Vs + (size_t)(j % NS) * KV_BYTES);
-          const uint32_t acc = tmem_base + (uint32_t)(2 * BN + b * D);
+          const uint32_t acc = tmem_base + (uint32_t)(2 * BN);
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk) {
-            const uint64_t dp = make_desc(pa + (uint32_t)((kk >> 2) * (BM * 128) + (kk & 3) * 32), 0);
+            const uint64_t dp = make_desc(pa + (uint32_t)(kk * 32), 0);
             const uint64_t dv = make_desc(va + (uint32_t)(kk * 2048), BN * 128);
-            tc_mma(acc, dp, dv, idesc_o, kk != 0 ? 1u : 0u);
+            tc_mma(acc, dp, dv, idesc_o, (j | kk) != 0 ? 1u : 0u);
           }
-          tc_commit(&o_full[b]);
+          tc_commit(&p_empty[b]);            // also: "the products up to tile j have finished"
           tc_commit(&kv_empty[j % NS]);
         }
       } while (false);
@@ -250,10 +289,9 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     const int tok = row_ok ? m / G : 0, head = row_ok ? hk * G + (m - tok * G) : 0;
     const int pos = row_ok ? p0 + tok : -1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha = 1.f;
+    const uint32_t o_addr = lane_addr + (uint32_t)(2 * BN);
+    float m_ref = -INFINITY;                             // what the exponentials are taken against (log2 domain)
+    float l_run = 0.f;
     const int first_pos = p0 + tok0;                     // smallest position of the tile's rows
 
     for (int j = 0; j < n_tiles && !failed; ++j) {
@@ -261,32 +299,49 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
       if (!mbar_wait(&s_full[b], (j >> 1) & 1)) { failed = true; break; }
       tc_fence_after();
       const bool masked = kt + BN - 1 > first_pos;       // the tile reaches beyond what the first row may see
-      // the whole row of scores in registers: four loads in flight, one wait
       float sv[BN];
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tc_load32(lane_addr + (uint32_t)(b * BN + c * 32), sv + c * 32);
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[b]);           // S of this tile has been read
-      float mx = -INFINITY;
+      if (lane == 0) mbar_arrive(&s_empty[b]);           // the scores are in registers: the buffer may be reused
       if (masked) {
 #pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          sv[i] = (kt + i <= pos) ? sv[i] : -INFINITY;
-          mx = fmaxf(mx, sv[i]);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sv[i]);
+        for (int i = 0; i < BN; ++i) sv[i] = (kt + i <= pos) ? sv[i] : -INFINITY;
       }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float use = (m_new == -INFINITY) ? 0.f : m_new;
-      alpha = ex2(m_run - use);
-      m_run = m_new;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BN; i += 4) {
+        mx0 = fmaxf(mx0, sv[i]); mx1 = fmaxf(mx1, sv[i + 1]); mx2 = fmaxf(mx2, sv[i + 2]); mx3 = fmaxf(mx3, sv[i + 3]);
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      // the reference follows the maximum only when that has run ahead by more than 8 (or there was none yet)
+      const bool moved = m_tile > m_ref + 8.0f;           // false for m_tile = -inf; true for m_ref = -inf, m_tile finite
+      if (__any_sync(0xffffffffu, moved && m_ref != -INFINITY)) {
+        // rare: rescale the accumulator in tensor memory, once the products issued so far (up to tile j-1) are done
+        const int pb = (j - 1) & 1;
+        if (!mbar_wait(&p_empty[pb], ((j - 1) >> 1) & 1)) { failed = true; break; }
+        tc_fence_after();
+        const float f = (moved && m_ref != -INFINITY) ? ex2(m_ref - m_tile) : 1.f;
+        float ov[D];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tc_load32(o_addr + (uint32_t)(c * 32), ov + c * 32);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < D; ++i) ov[i] *= f;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tc_store32(o_addr + (uint32_t)(c * 32), ov + c * 32);
+        tc_wait_st();
+        l_run *= f;
+      }
+      if (moved) m_ref = m_tile;                         // (with no reference yet, accumulator and sum are still zero)
+      const float use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      // the buffer of probabilities must have been read by the product of two tiles ago
+      if (j >= 2 && !mbar_wait(&p_empty[b], ((j - 2) >> 1) & 1)) { failed = true; break; }
       // probabilities -> shared memory (bfloat16, the swizzled K-major layout of the second product);
       // ex2(-inf) = 0 takes care of masked entries
-      float sum = 0.f;
+      float sum0 = 0.f, sum1 = 0.f;
       unsigned char* prow = Ps + (size_t)b * P_BYTES + (size_t)row * 128;
 #pragma unroll
       for (int c = 0; c < BN / 8; ++c) {                 // 16-byte pieces of 8 keys
@@ -295,59 +350,45 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
         for (int i = 0; i < 4; ++i) {
           const float e0 = ex2(fmaf(sv[c * 8 + 2 * i], p.scale_log2, -use));
           const float e1 = ex2(fmaf(sv[c * 8 + 2 * i + 1], p.scale_log2, -use));
-          sum += e0 + e1;
+          sum0 += e0;
+          sum1 += e1;
           pk[i] = pack_bf16(e0, e1);
         }
-        unsigned char* blk = prow + (size_t)(c >> 3) * (BM * 128);   // 64 keys to a k-block
-        *reinterpret_cast<uint4*>(blk + (((c & 7) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      l_run = l_run * alpha + sum;
+      l_run += sum0 + sum1;
       // values of keys beyond the sequence (never written, or another tile's leftovers) must not meet a zero
       // probability as NaN: the rows of this stage beyond hi are cleared
       if (kt + BN > hi) {
         if (!mbar_wait(&kv_full[j % NS], (j / NS) & 1)) { failed = true; break; }
         unsigned char* vt = Vs + (size_t)(j % NS) * KV_BYTES;
-        const int first = hi - kt;                       // rows [first, 128)
+        const int first = hi - kt;                       // rows [first, BN)
         for (int idx = (warp - 2) * 32 + lane; idx < (BN - first) * 8; idx += 128)
           *reinterpret_cast<uint4*>(vt + (size_t)(first + (idx >> 3)) * 128 + ((idx & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
       }
+      tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these writes are read by the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[b]);
-      // the finished O_tile of the tile before joins the accumulator; both were relative to the old maximum
-      if (j >= 1) {
-        const int pb = (j - 1) & 1;
-        if (!mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1)) { failed = true; break; }
-        tc_fence_after();
-        float v[D];
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) tc_load32(lane_addr + (uint32_t)(2 * BN + pb * D + c * 32), v + c * 32);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = (o[i] + v[i]) * alpha;
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&o_empty[pb]);
-      }
     }
     if (!failed) {
+      // all products have finished when the last one has
       const int pb = (n_tiles - 1) & 1;
-      if (!mbar_wait(&o_full[pb], ((n_tiles - 1) >> 1) & 1)) failed = true;
+      if (!mbar_wait(&p_empty[pb], ((n_tiles - 1) >> 1) & 1)) failed = true;
       tc_fence_after();
       if (!failed) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        uint32_t pk[D / 2];
-        float v[D];
+        float ov[D];
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) tc_load32(lane_addr + (uint32_t)(2 * BN + pb * D + c * 32), v + c * 32);
+        for (int c = 0; c < D / 32; ++c) tc_load32(o_addr + (uint32_t)(c * 32), ov + c * 32);
         tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < D / 2; ++i) pk[i] = pack_bf16((o[2 * i] + v[2 * i]) * inv, (o[2 * i + 1] + v[2 * i + 1]) * inv);
         if (row_ok) {
           bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)head * D;
 #pragma unroll
           for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+            *reinterpret_cast<uint4*>(dst + i * 8) =
+                make_uint4(pack_bf16(ov[8 * i] * inv, ov[8 * i + 1] * inv), pack_bf16(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv),
+                           pack_bf16(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv), pack_bf16(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv));
         }
       }
     }
@@ -387,7 +428,7 @@ SB_EXPORT int sb_attention_tc_supports(int H, int Hkv, int ps, int window, int q
   if (H <= 0 || Hkv <= 0 || H % Hkv) return 0;
   const int G = H / Hkv;
   if (G > 128 || (128 % G)) return 0;                   // a tile holds whole tokens: 128 / G of them
-  if (ps < 8 || ps > 128 || (128 % ps)) return 0;       // pages tile the 128-key stage, in whole swizzle atoms
+  if (ps < 8 || ps > BN || (BN % ps)) return 0;         // pages tile a stage of keys, in whole swizzle atoms
   if (window > 0) return 0;
   if (q_stride % 8) return 0;
   return 1;

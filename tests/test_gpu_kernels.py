@@ -463,3 +463,69 @@ def test_sizes_the_tcgen05_product_leaves_to_the_library(K):
     out = torch.empty(128, 100, device=DEV, dtype=torch.bfloat16)
     K.linear(a, w, out)
     torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=0.3, rtol=2e-2)
+
+
+TC_ATT_CASES = [
+    # heads, kv, page, q_lens, kv_lens
+    (4, 1, 64, [128], [128]),                              # one full tile of rows, one page
+    (4, 1, 64, [33], [33]),                                # a ragged tile
+    (32, 8, 64, [2048], [2048]),                           # the benchmark's shape
+    (32, 8, 16, [300, 1, 70], [300, 700, 500]),            # portions with a cached prefix beside a decoded token
+    (8, 8, 32, [130, 40], [130, 1000]),                    # no grouping
+    (16, 2, 8, [65, 17], [400, 17]),                       # group of 8, small pages
+    (64, 1, 64, [50], [777]),                              # group of 64: two tokens to a tile
+]
+
+
+@pytest.mark.parametrize("case", TC_ATT_CASES, ids=[f"h{c[0]}kv{c[1]}p{c[2]}n{len(c[3])}" for c in TC_ATT_CASES])
+def test_attention_tensor_memory_path(K, case):
+    """Prompt portions at head_dim 64 run on tcgen05 (TMA in, scores and output in tensor memory): against the
+    mma.sync kernel and the torch version, with unwritten cache rows poisoned."""
+    heads, kv_heads, page, q_lens, kv_lens = case
+    d = 64
+    lib = K._attention_lib(d)
+    assert lib.sb_attention_tc_supports(heads, kv_heads, page, 0, (heads + 2 * kv_heads) * d) == 1
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens, kv_lens)
+    for r, L in enumerate(kv_lens):                        # rows of the last page beyond the sequence: NaN
+        b = (L - 1) // page
+        if L % page:
+            s["kc"][int(s["bt"][r, b]), :, L % page:] = float("nan")
+            s["vc"][int(s["bt"][r, b]), :, L % page:] = float("nan")
+    t = sum(q_lens)
+    scale = 1.0 / math.sqrt(d)
+    outs = {}
+    for name in ("tc", "legacy", "torch"):
+        out = torch.full((t, heads * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        if name == "torch":
+            E.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, 0, out, s["shape"])
+        else:
+            K.use_tcgen05_attention = name == "tc"
+            try:
+                K.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, 0, out, s["shape"])
+            finally:
+                K.use_tcgen05_attention = True
+            K.check_errors()
+        outs[name] = out.float()
+    assert bool(torch.isfinite(outs["tc"]).all()), "a row was not written, or NaN"
+    torch.testing.assert_close(outs["tc"], outs["torch"], atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(outs["legacy"], outs["torch"], atol=2e-2, rtol=2e-2)
+
+
+def test_attention_tensor_memory_path_rescales_when_the_maximum_runs_ahead(K):
+    """The tcgen05 kernel keeps its output in tensor memory and rescales it only when a row's maximum has moved by
+    more than a factor 2^8. Here later keys score far higher than earlier ones, several times in a row."""
+    heads, kv_heads, d, page = 4, 1, 64, 64
+    L = 512
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, [L], [L], seed=7)
+    s["qkv"].mul_(0.1)
+    q = s["qkv"].view(L, heads + 2, d)
+    q[:, :heads, :4] = 3.0
+    for key in range(L):                                   # keys grow with their position: maxima keep moving
+        blk, off = key // page, key % page
+        s["kc"][int(s["bt"][0, blk]), 0, off, :4] = 0.02 * key
+    out = torch.full((L, heads * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ref = torch.empty_like(out)
+    K.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, 1.0, 0, out, s["shape"])
+    K.check_errors()
+    E.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, 1.0, 0, ref, s["shape"])
+    torch.testing.assert_close(out.float(), ref.float(), atol=3e-2, rtol=3e-2)
