@@ -148,6 +148,22 @@ def test_rope_cache_write(K, dtype, heads, kv_heads, d, rot, pairing, page):
     torch.testing.assert_close(c["qkv"].float(), b["qkv"].float(), **tol)
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,rot,page", [(8, 2, 64, 64, 64), (5, 1, 48, 32, 16), (4, 4, 128, 128, 8)])
+def test_rope_cache_write_many_tokens(K, heads, kv_heads, d, rot, page):
+    """Prompt portions with adjacent pairs take a vectorised kernel (8 elements per thread)."""
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens=[70, 1, 129], kv_lens=[70, 33, 300])
+    inv = (1.0 / (10000.0 ** (torch.arange(0, rot, 2).float() / rot))).to(DEV)
+    a = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in s.items()}
+    b = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in s.items()}
+    K.rope_cache_write(a["qkv"], a["pos"], a["row"], inv, 1, rot, heads, kv_heads, d, a["kc"], a["vc"], a["bt"], page, True)
+    E.rope_cache_write(b["qkv"], b["pos"], b["row"], inv, 1, rot, heads, kv_heads, d, b["kc"], b["vc"], b["bt"], page, True)
+    K.check_errors()
+    q_cols = heads * d
+    torch.testing.assert_close(a["qkv"][:, :q_cols].float(), b["qkv"][:, :q_cols].float(), atol=4e-2, rtol=2e-2)
+    torch.testing.assert_close(a["kc"].float(), b["kc"].float(), atol=4e-2, rtol=2e-2)
+    assert torch.equal(a["vc"], b["vc"])
+
+
 def test_rotation_at_large_positions(K):
     """Angles are float32 products of position and frequency; at position 100000 a lost bit would show."""
     heads, kv_heads, d = 2, 1, 64
