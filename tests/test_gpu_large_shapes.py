@@ -1,0 +1,68 @@
+"""The engine at the benchmark's layer sizes (Llama-3.2-1B widths, two layers, a smaller vocabulary) against the plain
+implementation: only at these sizes do prompt portions run on the tcgen05 kernels (products with >= 96 tiles,
+attention at head_dim 64) and decoding on the fused few-rows kernels with their real widths."""
+import pytest
+import torch
+
+from tests import helpers
+from tests.plain.llama_plain import llama_forward
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, num_hidden_layers=2, num_attention_heads=32,
+           num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=8192, rms_norm_eps=1e-5, rope_theta=500000.0,
+           rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                             original_max_position_embeddings=8192),
+           tie_word_embeddings=True, max_position_embeddings=131072)
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    from serve_b200.config import config_from_dict
+    from serve_b200.weights import write_random_model
+
+    folder = str(tmp_path_factory.mktemp("big"))
+    write_random_model(folder, config_from_dict(CFG), seed=11, std=0.02, norm_std=0.05, dtype=torch.bfloat16)
+    cfg, w = helpers.read_folder(folder)
+    reqs = {"long": helpers.random_tokens(cfg["vocab_size"], 1600, seed=1), "short": helpers.random_tokens(cfg["vocab_size"], 300, seed=2)}
+    with torch.no_grad():
+        plain = {rid: llama_forward(w, cfg, toks) for rid, toks in reqs.items()}
+    return folder, reqs, plain
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_benchmark_widths_match_plain(big, dtype):
+    from serve_b200.config import EngineConfig
+    from serve_b200.engine import Engine
+
+    folder, reqs, plain = big
+    eng = Engine.from_folder(folder, EngineConfig(dtype=dtype, page_size=64, num_pages=64, max_slots=4, max_tokens_per_step=2048,
+                                                  max_context=2048, use_cuda_graphs=True))
+    # the long prompt whole (tcgen05 products and attention in bfloat16), then the short one in portions beside
+    # decoded tokens of the long one, then both decoding from graphs
+    steps = [{"step": 0, "entries": [{"id": "long", "tokens": reqs["long"][:1500], "want": [0, 700, 1499]}], "end": []}]
+    at_long, at_short = 1500, 0
+    for n in (130, 64, 90, 16):
+        take = min(n, 300 - at_short)
+        steps.append({"step": len(steps), "entries": [
+            {"id": "long", "tokens": [reqs["long"][at_long]], "want": [0]},
+            {"id": "short", "tokens": reqs["short"][at_short:at_short + take], "want": [take - 1]}], "end": []})
+        at_long += 1
+        at_short += take
+    assert at_short == 300
+    for _ in range(12):
+        steps.append({"step": len(steps), "entries": [{"id": "long", "tokens": [reqs["long"][at_long]], "want": [0]}], "end": []})
+        at_long += 1
+    launches_before = eng.kernels.launches
+    library_before = eng.kernels.library_calls
+    with torch.inference_mode():
+        got = helpers.replay(eng, steps)
+    eng.kernels.check_errors()
+    scale = max(float(p.abs().max()) for p in plain.values())
+    helpers.compare_with_plain(got, plain, atol=scale * 2.0 ** -6 if dtype == "bfloat16" else 2e-4)
+    if dtype == "bfloat16":
+        assert eng.stepper.launched_graphs >= 10
+        assert eng.kernels.launches > launches_before
+        # the whole-prompt step keeps its products on this engine's kernels (only the mixed steps' 65..131-row
+        # products go to the library)
+        assert eng.kernels.library_calls - library_before < 40
