@@ -252,6 +252,196 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The same product with two CTAs (a cluster of two, on neighbouring SMs) working on one 256 x bn tile:
+// tcgen05.mma.cta_group::2. CTA r of the pair holds rows 128 r .. 128 r + 127 of the tile's a operand and the r-th
+// half of its w operand in its own shared memory, and its 128 rows of the accumulator in its own tensor memory.
+// One thread of the first CTA issues the products for both; each product reads both shared memories, so every CTA
+// loads (and the tensor core reads) only half of w per tile: shared-memory traffic per flop is 2/3 of the
+// one-CTA kernel's, which is what that kernel is bound by. A stage is 16 KB of a + at most 16 KB of w, six stages.
+//
+// Barriers: both CTAs' TMA loads count their bytes on the first CTA's full barrier (its address with the pair bit
+// cleared); tcgen05.commit arrives on the empty / accumulator-full barriers of both CTAs at once (multicast);
+// the epilogue warps of both CTAs arrive on the first CTA's accumulator-empty barrier (a remote arrive for the second).
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_A_BYTES = 128 * BK * 2, PAIR_STAGE_BYTES = PAIR_A_BYTES + 128 * BK * 2;
+constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;   // clears the bit of a shared-memory address that tells the two CTAs apart
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, once the products issued so far are done, on the barrier at this address in both CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all_threads() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
+template <bool GU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
+    gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                             bf16* __restrict__ out, int M, int N, int K, int bn, int* __restrict__ error) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[PAIR_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[PAIR_STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int OUT_COLS = GU ? bn / 2 : bn;
+  const int half = bn / 2;                              // rows of w this CTA loads per stage
+  const int m_tiles = (M + 255) / 256, n_tiles = (N + OUT_COLS - 1) / OUT_COLS;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);       // one arrival per epilogue warp of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+  }
+  if (warp == 1) {
+    // the same warp of both CTAs allocates: the accumulators get the same address in both tensor memories
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all_threads();            // the other CTA's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = pair; tile < total_tiles && !failed; tile += num_pairs) {
+        const int m0 = (tile % m_tiles) * 256 + (int)rank * 128, n0 = (tile / m_tiles) * OUT_COLS;
+        // with gate_up the first CTA loads the gate rows and the second their up rows: accumulator columns
+        // 0 .. half-1 are gate, half .. bn-1 are up, for the rows of both CTAs
+        const int w_row = GU ? (rank == 0 ? n0 : N + n0) : n0 + (int)rank * half;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % PAIR_STAGES;
+          if (!mbar_wait(&empty_bar[s], ((it / PAIR_STAGES) & 1) ^ 1)) { failed = true; break; }
+          unsigned char* a_dst = tiles + (size_t)s * PAIR_STAGE_BYTES;
+          const uint32_t leader_bar = smem_u32(&full_bar[s]) & PAIR_LEADER_MASK;
+          if (rank == 0) mbar_expect_tx(&full_bar[s], (unsigned)(2 * (PAIR_A_BYTES + half * BK * 2)));
+          tma_load_2d_pair(a_dst, &map_a, leader_bar, kb * BK, m0);
+          tma_load_2d_pair(a_dst + PAIR_A_BYTES, &map_w, leader_bar, kb * BK, w_row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(256, bn);
+      int it = 0, local = 0;
+      for (int tile = pair; tile < total_tiles && !failed; tile += num_pairs, ++local) {
+        const int buf = local & 1;
+        if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % PAIR_STAGES;
+          if (!mbar_wait(&full_bar[s], (it / PAIR_STAGES) & 1)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * PAIR_STAGE_BYTES);
+          const uint64_t da = make_desc(a_addr), db = make_desc(a_addr + PAIR_A_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j)
+            tc_mma_pair(acc, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kb | j) != 0 ? 1u : 0u);
+          tc_commit_pair(&empty_bar[s]);
+        }
+        tc_commit_pair(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t leader_acc_empty[2];
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_acc_empty[b]) : "r"(smem_u32(&acc_empty[b])), "r"(0u));
+    int local = 0;
+    for (int tile = pair; tile < total_tiles && !failed; tile += num_pairs, ++local) {
+      const int m0 = (tile % m_tiles) * 256 + (int)rank * 128, n0 = (tile / m_tiles) * OUT_COLS;
+      const int buf = local & 1;
+      if (!mbar_wait(&acc_full[buf], (local >> 1) & 1)) { failed = true; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+      for (int c = 0; c < OUT_COLS; c += 32) {
+        if (n0 + c >= N) break;
+        uint32_t v[32];
+        tc_load32(acc + (uint32_t)c, v);
+        uint32_t packed[16];
+        if (GU) {
+          uint32_t u[32];
+          tc_load32(acc + (uint32_t)(OUT_COLS + c), u);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float g0 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i]))), g1 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i + 1])));
+            const float u0 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i]))), u1 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i + 1])));
+            __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            packed[i] = *reinterpret_cast<uint32_t*>(&o);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            packed[i] = *reinterpret_cast<uint32_t*>(&o);
+          }
+        }
+        if (row < M) {
+          bf16* dst = out + (size_t)row * N + n0 + c;
+          if (n0 + c + 32 <= N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (n0 + c + i < N) dst[i] = reinterpret_cast<const bf16*>(packed)[i];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(leader_acc_empty[buf]) : "memory");
+    }
+  }
+  if (failed) atomicExch(error, 1);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all_threads();            // neither CTA leaves, or frees tensor memory, while the other may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -275,7 +465,40 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
   return r == CUDA_SUCCESS ? 0 : -301 - (int)r;
 }
 
+int g_pair_enabled = 1;
+int g_pair_capacity[2] = {0, 0};
+
+bool pair_mode(int M) { return g_pair_enabled && M > 128; }
+
+// CTA pairs of the two-CTA kernel that the device holds at a time (the persistent grid's size)
+int pair_capacity(bool gate_up, int sms) {
+  int& cached = g_pair_capacity[gate_up ? 1 : 0];
+  if (cached > 0) return cached;
+  const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sms / 2 * 2, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  int clusters = 0;
+  cudaError_t e;
+  if (gate_up) {
+    cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<true>, &cfg);
+  } else {
+    cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<false>, &cfg);
+  }
+  if (e != cudaSuccess || clusters < 1) { cudaGetLastError(); clusters = sms / 2; }
+  if (clusters > sms / 2) clusters = sms / 2;
+  cached = clusters;
+  return cached;
+}
+
 }  // namespace
+
+// Tests: 0 keeps every product on the one-CTA kernel, 1 (the default) sends tiles of more than 128 rows to CTA pairs.
+SB_EXPORT void sb_gemm_tcgen05_use_pairs(int on) { g_pair_enabled = on; }
+SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(gate_up != 0, 148); }
 
 // 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).
 SB_EXPORT int sb_gemm_tcgen05_supports(int M, int N, int K, int gate_up) {
@@ -298,8 +521,31 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  // accumulator columns per tile: the width whose tiles need the least time in whole waves of one CTA per SM
-  // (time of a wave ~ tile width, plus a fixed part of about 32 columns' worth)
+  if (pair_mode(M)) {
+    // two CTAs per 256-row tile: as below, the width whose tiles need the least time in whole waves of CTA pairs
+    const long long m_tiles = (M + 255) / 256;
+    const int pairs = pair_capacity(gate_up != 0, sms);
+    int bn = BN;
+    if (!gate_up) {
+      long long best = -1;
+      for (int cand = BN; cand >= 128; cand -= 32) {
+        const long long n_tiles = (N + cand - 1) / cand;
+        const long long waves = (m_tiles * n_tiles + pairs - 1) / pairs;
+        const long long cost = waves * (cand + 32);
+        if (best < 0 || cost < best) { best = cost; bn = cand; }
+      }
+    }
+    rc = make_map(&map_w, w, (uint64_t)(gate_up ? 2 * N : N), (uint64_t)K, bn / 2);
+    if (rc) return rc;
+    const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+    const int out_cols = gate_up ? bn / 2 : bn;
+    const long long tiles = (long long)((N + out_cols - 1) / out_cols) * m_tiles;
+    dim3 grid((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
+    if (gate_up) gemm_tcgen05_pair_kernel<true><<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
+    else gemm_tcgen05_pair_kernel<false><<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   const long long m_tiles = (M + BM - 1) / BM;
   int bn = BN;
   if (!gate_up) {

@@ -412,8 +412,16 @@ def test_sizes_the_skinny_kernel_leaves_to_the_library(K):
 TC_SHAPES = [(128, 128, 64), (256, 256, 256), (2048, 3072, 2048), (300, 264, 200), (64, 136, 72), (1000, 2048, 8192), (129, 8, 8)]
 
 
-@pytest.mark.parametrize("m,n,k", TC_SHAPES)
-def test_tcgen05_product(K, m, n, k):
+@pytest.fixture(params=["pairs", "single"])
+def cta_mode(K, request):
+    """Tiles of more than 128 rows run on CTA pairs (cta_group::2) by default; "single" keeps them on the one-CTA kernel."""
+    K._core.sb_gemm_tcgen05_use_pairs(1 if request.param == "pairs" else 0)
+    yield request.param
+    K._core.sb_gemm_tcgen05_use_pairs(1)
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES + [(257, 520, 136), (4096, 512, 64), (777, 2048, 1000)])
+def test_tcgen05_product(K, m, n, k, cta_mode):
     """The tensor-memory product (TMA in, tcgen05.mma, tcgen05.ld out) against float64: full tiles, ragged edges in every
     dimension, k not a multiple of the stage, a single partial tile."""
     a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
@@ -450,7 +458,7 @@ def test_tcgen05_product(K, m, n, k):
 
 
 @pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (2048, 8192, 2048), (300, 384, 200), (130, 128, 72), (64, 256, 96)])
-def test_tcgen05_gate_up_with_swiglu(K, m, inter, k):
+def test_tcgen05_gate_up_with_swiglu(K, m, inter, k, cta_mode):
     h = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * inter, k, device=DEV) * 0.05).to(torch.bfloat16)
     fused = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
