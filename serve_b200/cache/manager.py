@@ -95,6 +95,7 @@ class CacheManager:
                                           PagePool(num_pages, len(self.groups)),
                                           np.full((max_slots, self.max_blocks), -1, dtype=np.int32)))
             self._entry_group.append(key_to_group[key])
+        self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None]   # groups that give pages back early
         self._free_slots: List[int] = list(range(max_slots - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
         self._needs = list(needs)
@@ -194,20 +195,31 @@ class CacheManager:
 
     def reserve(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
         """Give every listed request pages up to its new length, or raise OutOfPages and change nothing."""
-        want = [0] * len(self.groups)
+        n_groups = len(self.groups)
+        want = [0] * n_groups
+        grow = []                                   # (request, rid, blocks it must reach): only those that need pages
+        ps, limit, requests = self.page_size, self.max_context, self._requests
         for rid, new_len in batch:
-            if new_len > self.max_context:
-                raise ValueError(f"request {rid!r} would reach {new_len} tokens; the context limit is {self.max_context}")
-            if new_len < self._requests[rid].length:
-                raise ValueError(f"request {rid!r} cannot shrink from {self._requests[rid].length} to {new_len}")
-            want = [a + b for a, b in zip(want, self.pages_wanted(rid, new_len))]
+            r = requests[rid]
+            if new_len > limit:
+                raise ValueError(f"request {rid!r} would reach {new_len} tokens; the context limit is {limit}")
+            if new_len < r.length:
+                raise ValueError(f"request {rid!r} cannot shrink from {r.length} to {new_len}")
+            nb = -(-new_len // ps)
+            grows = False
+            for gi in range(n_groups):
+                d = nb - r.reserved[gi]
+                if d > 0:
+                    want[gi] += d
+                    grows = True
+            if grows:
+                grow.append((r, rid, nb))
         for w, g in zip(want, self.groups):
             if w > g.pool.available:
                 raise OutOfPages(w, g.pool.available, g.pool.group)
-        for rid, new_len in batch:
-            r = self._requests[rid]
+        for r, rid, nb in grow:
             for gi, g in enumerate(self.groups):
-                n = self.blocks_for(new_len) - r.reserved[gi]
+                n = nb - r.reserved[gi]
                 if n > 0:
                     pages = g.pool.take(n, rid)
                     g.table[r.slot, r.reserved[gi]: r.reserved[gi] + n] = pages
@@ -217,7 +229,8 @@ class CacheManager:
         """The request now holds new_len tokens; pages a window has passed go back to the pool."""
         r = self._requests[rid]
         r.length = new_len
-        for gi, g in enumerate(self.groups):
+        for gi in self._windowed:
+            g = self.groups[gi]
             first = min(self._first_needed_block(g, new_len), r.reserved[gi])
             if first > r.released[gi]:
                 pages = [int(p) for p in g.table[r.slot, r.released[gi]: first]]

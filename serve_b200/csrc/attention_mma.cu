@@ -73,6 +73,8 @@ struct Params {
   float* part_o;    // [R, Hkv, splits, 16, D]
   float* part_ml;   // [R, Hkv, splits, 16, 2]
   int* tickets;     // [R, Hkv] zero before the launch and again after it; nullptr: a separate kernel merges
+  // wide shape only
+  const int* wide_rows;   // requests the launch covers (blockIdx.z indexes it); nullptr: all, in order
 };
 
 constexpr int MAX_SPLITS = 32;
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [BM][LDS]
   bf16* KVs = Qs + BM * LDS;                        // 2 stages x (K [BN][LDS], V [BN][LDS])
 
-  const int r = blockIdx.z, hk = blockIdx.y;
+  const int r = p.wide_rows ? p.wide_rows[blockIdx.z] : (int)blockIdx.z, hk = blockIdx.y;
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int G = p.G;
   const int M = qn * G;                             // rows of this (request, kv head)
@@ -700,13 +702,15 @@ SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_
   return (long long)n_rows * Hkv * num_splits * 16 * (D + 2) * (long long)sizeof(float);
 }
 
-// which: bit 0 launch the wide shape, bit 1 launch the deep shape. With num_splits > 1 the deep shape needs
+// which: bit 0 launch the wide shape (for the n_wide requests listed in wide_rows if that is given, else for all:
+// a step of hundreds of decoding requests and a few prompt portions then launches blocks for the portions only),
+// bit 1 launch the deep shape. With num_splits > 1 the deep shape needs
 // ``scratch`` (sb_attention_mma_scratch_bytes) and merges either in the block that finishes last (tickets: n_rows * Hkv
 // ints, zero before the first launch; every launch leaves them zero) or, with tickets == nullptr, in a second kernel.
 SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
                                const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
                                void* out, int n_rows, int max_q, int which, int split_size, int num_splits, void* scratch,
-                               int* tickets, cudaStream_t stream) {
+                               int* tickets, const int* wide_rows, int n_wide, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -717,13 +721,15 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
   p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+  p.wide_rows = wide_rows;
   if (which & 1) {
     auto k = attention_wide_kernel;
     const size_t smem = wide_smem_bytes();
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const long long tiles = ((long long)max_q * p.G + 63) / 64;
     if (tiles > 2147483647LL) return SB_ERR_LIMIT;
-    k<<<dim3((unsigned)tiles, Hkv, n_rows), THREADS, smem, stream>>>(p);
+    const int z = wide_rows ? n_wide : n_rows;
+    if (z > 0) k<<<dim3((unsigned)tiles, Hkv, z), THREADS, smem, stream>>>(p);
     SB_LAUNCH_CHECK();
   }
   if (which & 2) {
@@ -800,6 +806,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+  p.wide_rows = nullptr;
   if (num_splits > 1) {
     p.part_o = scratch;
     p.part_ml = scratch + (size_t)n_rows * Hkv * num_splits * 16 * D;

@@ -142,12 +142,13 @@ struct TcParams {
   float scale_log2;
   bf16* out;
   int* error;
+  const int* rows;      // requests this launch covers (blockIdx.z indexes it); nullptr: all, in order
 };
 
 __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v, const TcParams p) {
-  const int r = blockIdx.z, hk = blockIdx.y;
+  const int r = p.rows ? p.rows[blockIdx.z] : (int)blockIdx.z, hk = blockIdx.y;
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int G = p.G;
   const int M = qn * G;
@@ -435,10 +436,11 @@ SB_EXPORT int sb_attention_tc_supports(int H, int Hkv, int ps, int window, int q
 }
 
 // The wide shape of sb_attention_mma (requests with more than 16 rows) on tcgen05; arguments as there.
-// n_tokens: rows of qkv; num_pages: pages of kc / vc.
+// n_tokens: rows of qkv; num_pages: pages of kc / vc. rows (may be null): the n_rows requests to cover, so that a
+// step of hundreds of decoding requests and a few prompt portions launches blocks for the portions only.
 SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const void* kc, const void* vc, const int* block_table,
                               int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale,
-                              void* out, int n_rows, int max_q, int* error, cudaStream_t stream) {
+                              void* out, int n_rows, int max_q, const int* rows, int* error, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (!sb_attention_tc_supports(H, Hkv, ps, 0, q_stride)) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -463,7 +465,7 @@ SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const
   }
   TcParams p;
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
-  p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.scale_log2 = scale * LOG2E; p.out = (bf16*)out; p.error = error;
+  p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.scale_log2 = scale * LOG2E; p.out = (bf16*)out; p.error = error; p.rows = rows;
   const int tok_per_tile = BM / G;
   const int m_tiles = (max_q + tok_per_tile - 1) / tok_per_tile;
   auto k = attention_tc_kernel;

@@ -121,8 +121,7 @@ class Scheduler:
         (they are listed in ``self.evicted`` for the caller to close in the cache)."""
         self.evicted = []
         while True:
-            entries = self._plan_running()
-            need = self._new_pages(entries)
+            entries, need = self._plan_running()
             if need <= self._free_pages() + self._pages_of(self.evicted):
                 break
             # pages ran out: the request admitted last goes back to the head of the queue
@@ -146,22 +145,34 @@ class Scheduler:
         self.evicted.append(victim)
         self.waiting.appendleft(victim)
 
-    def _plan_running(self) -> List[PlannedEntry]:
+    def _plan_running(self):
+        """(entries of the running requests, cache pages they need beyond what they hold)."""
         entries: List[PlannedEntry] = []
         left = self.budget
-        # decoding requests first: one token each
+        ps = self.cache.page_size
+        need = 0
+        portions = []
+        # decoding requests first: one token each (this loop runs for every live request in every step)
         for r in self.running:
-            if r.sequence_length - r.fed == 1 and left > 0:
-                entries.append(PlannedEntry(r, r.pending(), True))
-                left -= 1
+            gen = r.generated
+            n = len(r.prompt) + len(gen) - r.fed
+            if n == 1:
+                if left > 0:
+                    tok = gen[-1] if gen else r.prompt[-1]
+                    entries.append(PlannedEntry(r, [FROM_DEVICE if tok is None else tok], True))
+                    left -= 1
+                    if r.fed % ps == 0:
+                        need += 1                   # its token opens a new page
+            elif n > 1:
+                portions.append((r, n))
         # then portions of prompts already under way
-        for r in self.running:
-            n = r.sequence_length - r.fed
-            if n > 1 and left > 0:
+        for r, n in portions:
+            if left > 0:
                 take = min(n, self.prefill_chunk, left)
                 entries.append(PlannedEntry(r, r.pending()[:take], take == n))
                 left -= take
-        return entries
+                need += -(-(r.fed + take) // ps) - -(-r.fed // ps)
+        return entries, need
 
     def _new_pages(self, entries: Sequence[PlannedEntry]) -> int:
         need = 0

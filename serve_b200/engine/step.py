@@ -11,6 +11,7 @@ replaces both.
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -39,6 +40,11 @@ class BatchShape:
     min_q: int         # fewest tokens any request brings
     max_kv: int        # longest sequence after the step
     pure_decode: bool  # every request brings exactly one token
+    # Requests ordered by how many tokens they bring, most first: their indices on the device, and the negated counts
+    # on the host (ascending, for bisect). A kernel that serves only requests with more than n tokens launches blocks
+    # for the first bisect_left(neg_q_sorted, -n) entries of rows_by_q. None: not given.
+    rows_by_q: object = None
+    neg_q_sorted: Optional[tuple] = None
 
 
 @dataclass
@@ -68,7 +74,7 @@ class _Layout:
         off = 0
         self.spans: Dict[str, tuple] = {}
         for name, n in (("tokens", t), ("positions", t), ("token_row", t), ("cu_q", r + 1), ("kv_len", r),
-                        ("slots", r), ("logit_rows", l)):
+                        ("slots", r), ("logit_rows", l), ("rows_by_q", r)):
             self.spans[name] = (off, n)
             off += _align4(max(n, 1))
         self.tables = []
@@ -99,6 +105,11 @@ class Stepper:
         self.last_h2d_bytes = 0
         self.last_slots = None      # device view of the state slots of the last step's rows
 
+    def _pinned_stream(self):
+        """The kernels object may look the current stream up once for a whole forward pass."""
+        pin = getattr(self.rt.kernels, "on_current_stream", None)
+        return pin() if pin is not None else contextlib.nullcontext()
+
     # ---- buffers ----------------------------------------------------------
     def _buffers(self, n: int):
         self._turn ^= 1
@@ -125,8 +136,6 @@ class Stepper:
         batch = []
         total = 0
         for e in entries:
-            if e.rid in seen:
-                raise ValueError(f"request {e.rid!r} appears twice in one step")
             seen.add(e.rid)
             n = len(e.tokens)
             if n == 0:
@@ -135,6 +144,8 @@ class Stepper:
                 if not (0 <= w < n):
                     raise ValueError(f"request {e.rid!r} wants place {w} of {n} tokens")
             total += n
+        if len(seen) != len(entries):
+            raise ValueError("a request appears twice in one step")
         if total > self.max_tokens_per_step:
             raise ValueError(f"the step holds {total} tokens; the limit is {self.max_tokens_per_step}")
         opened = []
@@ -209,6 +220,14 @@ class Stepper:
         h[cu_o: cu_o + r + 1] = cu
         h[kv_o: kv_o + r] = new_lens
         h[sl_o: sl_o + r] = [self.cache.slot(rid) for rid in rids]
+        rq_o, _ = lay.spans["rows_by_q"]
+        if pure_decode:
+            h[rq_o: rq_o + r] = row_of
+            neg_q_sorted = None
+        else:
+            order = np.argsort(-ql, kind="stable")
+            h[rq_o: rq_o + r] = order
+            neg_q_sorted = tuple((-ql[order]).tolist())
         if n_want:
             if pure_decode and n_want == r:
                 h[lr_o: lr_o + r] = np.arange(r)
@@ -228,7 +247,8 @@ class Stepper:
 
         ctx = StepContext(
             rt=self.rt,
-            shape=BatchShape(r, t, max(q_lens), min(q_lens), max(new_lens), pure_decode),
+            shape=BatchShape(r, t, max(q_lens), min(q_lens), max(new_lens), pure_decode,
+                             rows_by_q=view("rows_by_q") if neg_q_sorted is not None else None, neg_q_sorted=neg_q_sorted),
             tokens=view("tokens"), positions=view("positions"), token_row=view("token_row"),
             cu_q=view("cu_q"), kv_len=view("kv_len"), slots=view("slots"), logit_rows=view("logit_rows"),
             block_tables=[dev[off: off + rr * w].view(rr, w) for off, rr, w in lay.tables],
@@ -238,7 +258,8 @@ class Stepper:
         if graphable:
             logits = self._run_graph(ctx, r, max(new_lens))
         else:
-            logits = self.model.forward(ctx, self.views)
+            with self._pinned_stream():
+                logits = self.model.forward(ctx, self.views)
         for rid, n in batch:
             self.cache.commit(rid, n)
         return logits
@@ -262,13 +283,13 @@ class Stepper:
             # warm up outside capture (allocator pools, cuBLAS workspaces, lazy module loads)
             s = torch.cuda.Stream(device=self.rt.device)
             s.wait_stream(torch.cuda.current_stream(self.rt.device))
-            with torch.cuda.stream(s):
+            with torch.cuda.stream(s), self._pinned_stream():
                 self.model.forward(static_ctx, self.views)
             torch.cuda.current_stream(self.rt.device).wait_stream(s)
             graph = torch.cuda.CUDAGraph()
             k = self.rt.kernels
             before = (getattr(k, "launches", 0), getattr(k, "library_calls", 0))
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph), self._pinned_stream():
                 out = self.model.forward(static_ctx, self.views)
             counts = (getattr(k, "launches", 0) - before[0], getattr(k, "library_calls", 0) - before[1])
             g = (graph, out, self._dev, counts)

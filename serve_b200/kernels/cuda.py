@@ -5,6 +5,7 @@ refuses a size, the call raises. Calls launch on torch's current stream.
 """
 from __future__ import annotations
 
+import bisect
 import ctypes
 from typing import Dict, Optional
 
@@ -42,6 +43,23 @@ def _p(t: Optional[torch.Tensor]):
 
 def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _PinnedStream:
+    """While active, the kernels launch on the given stream handle without asking torch for the current stream at
+    every launch (that question costs several microseconds, a hundred times a step)."""
+
+    def __init__(self, kernels, handle):
+        self.kernels, self.handle, self.before = kernels, handle, None
+
+    def __enter__(self):
+        self.before = self.kernels._stream_handle
+        self.kernels._stream_handle = ctypes.c_void_p(self.handle) if self.handle is not None else None
+        return self
+
+    def __exit__(self, *exc):
+        self.kernels._stream_handle = self.before
+        return False
 
 
 def core_jobs():
@@ -87,11 +105,25 @@ class CudaKernels:
         self.use_tcgen05 = True             # tests: False keeps many-row products in the library
         self.fuse_rope = True               # tests: False runs the rotary kernel after the q/k/v product
         self.use_tcgen05_attention = True   # tests: False keeps prompt portions on the mma.sync kernel
+        self._stream_handle = None           # set by on_current_stream(): the stream every launch goes to
+        self._routes: Dict[tuple, int] = {}  # which product kernel takes a shape (asked of the libraries once)
+        self._tc_attention_ok: Dict[tuple, bool] = {}
+        self._split_scratch = None           # partial results of the split-key merge
         self._sample_work = None
         self._keep = []
         self._tickets = []                   # zeroed int32 buffers of the split-key merge (kept alive for graphs)
         self.launches = 0         # launches of this engine's own kernels
         self.library_calls = 0    # library matrix products
+
+    # ---- stream -----------------------------------------------------------
+    def on_current_stream(self):
+        """Context manager: look torch's current stream up once and launch on it until the block ends.
+        Enter it again after switching streams (graph capture does)."""
+        return _PinnedStream(self, torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _s(self):
+        h = self._stream_handle
+        return h if h is not None else ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
     # ---- checks -----------------------------------------------------------
     @staticmethod
@@ -147,49 +179,66 @@ class CudaKernels:
         self.launches += 1
         _check(self._core.sb_embedding(_p(tokens), _p(table), _p(out), tokens.shape[0], table.shape[1], table.shape[0],
                                        _DT[table.dtype], _p(last_token), last_token.shape[0] if last_token is not None else 0,
-                                       _stream()), "embedding")
+                                       self._s()), "embedding")
 
     def add_rmsnorm(self, x, delta, weight, eps, out) -> None:
         self.launches += 1
         _check(self._core.sb_add_rmsnorm(_p(x), _p(delta), _p(None), _p(weight), _DT[weight.dtype], _p(out), x.shape[0],
-                                         x.shape[1], ctypes.c_float(eps), _DT[out.dtype], _stream()), "add_rmsnorm")
+                                         x.shape[1], ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_rmsnorm")
 
     def add_rmsnorm_rows(self, x, delta, rows, weight, eps, out) -> None:
         self.launches += 1
         _check(self._core.sb_add_rmsnorm(_p(x), _p(delta), _p(rows), _p(weight), _DT[weight.dtype], _p(out), rows.shape[0],
-                                         x.shape[1], ctypes.c_float(eps), _DT[out.dtype], _stream()), "add_rmsnorm_rows")
+                                         x.shape[1], ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_rmsnorm_rows")
 
     def linear(self, a, w, out) -> None:
         """out[M,N] = a[M,K] @ w[N,K]^T (library matrix product)."""
         if a.dtype != w.dtype or a.shape[1] != w.shape[1] or out.shape[0] != a.shape[0] or out.shape[1] != w.shape[0]:
             raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} do not fit")
         m, n, k = a.shape[0], w.shape[0], a.shape[1]
-        if a.dtype == torch.bfloat16 and self.use_skinny_linear and self._core.sb_skinny_linear_supports(m, n, k, 0):
+        key = (a.dtype, out.dtype, m, n, k, self.use_skinny_linear, self.use_tcgen05, self.TCGEN05_MIN_TILES, 0)
+        route = self._routes.get(key)
+        if route is None:
+            route = 0
+            if a.dtype == torch.bfloat16 and self.use_skinny_linear and self._core.sb_skinny_linear_supports(m, n, k, 0):
+                route = 1
+            elif (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self._tcgen05_worthwhile(m, n)
+                    and self._core.sb_gemm_tcgen05_supports(m, n, k, 0)):
+                route = 2
+            self._routes[key] = route
+        if route == 1:
             self.launches += 1
-            _check(self._core.sb_skinny_linear(_p(a), _p(w), _p(out), m, n, k, _DT[out.dtype], 0, _stream()), "skinny linear")
-            return
-        if (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self._tcgen05_worthwhile(m, n)
-                and self._core.sb_gemm_tcgen05_supports(m, n, k, 0)):
+            _check(self._core.sb_skinny_linear(_p(a), _p(w), _p(out), m, n, k, _DT[out.dtype], 0, self._s()), "skinny linear")
+        elif route == 2:
             self.launches += 1
-            _check(self._core.sb_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, 0, self._wait_flag(), _stream()), "tcgen05 product")
-            return
-        self.library_calls += 1
-        _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), m, n, k, _DT[a.dtype], _DT[out.dtype], _stream()), "linear")
+            _check(self._core.sb_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, 0, self._wait_flag(), self._s()), "tcgen05 product")
+        else:
+            self.library_calls += 1
+            _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), m, n, k, _DT[a.dtype], _DT[out.dtype], self._s()), "linear")
 
     def gate_up_swiglu(self, h, w_gate_up, out) -> None:
         """out[T, I] = silu(h @ w_gate^T) * (h @ w_up^T), w_gate_up = [w_gate; w_up] of shape [2I, K]."""
         t, inter, k = h.shape[0], out.shape[1], h.shape[1]
         if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != k or out.shape[0] != t:
             raise KernelError("gate_up_swiglu: shapes do not fit")
-        if h.dtype == torch.bfloat16 and self.use_skinny_linear and self._core.sb_skinny_linear_supports(t, inter, k, 1):
+        key = (h.dtype, out.dtype, t, inter, k, self.use_skinny_linear, self.use_tcgen05, self.TCGEN05_MIN_TILES, 1)
+        route = self._routes.get(key)
+        if route is None:
+            route = 0
+            if h.dtype == torch.bfloat16 and self.use_skinny_linear and self._core.sb_skinny_linear_supports(t, inter, k, 1):
+                route = 1
+            elif (h.dtype == torch.bfloat16 and self._tcgen05_worthwhile(t, 2 * inter)
+                    and self._core.sb_gemm_tcgen05_supports(t, inter, k, 1)):
+                route = 2
+            self._routes[key] = route
+        if route == 1:
             self.launches += 1
-            _check(self._core.sb_skinny_linear(_p(h), _p(w_gate_up), _p(out), t, inter, k, _DT[out.dtype], 1, _stream()),
+            _check(self._core.sb_skinny_linear(_p(h), _p(w_gate_up), _p(out), t, inter, k, _DT[out.dtype], 1, self._s()),
                    "skinny gate/up")
             return
-        if (h.dtype == torch.bfloat16 and self._tcgen05_worthwhile(t, 2 * inter)
-                and self._core.sb_gemm_tcgen05_supports(t, inter, k, 1)):
+        if route == 2:
             self.launches += 1
-            _check(self._core.sb_gemm_tcgen05(_p(h), _p(w_gate_up), _p(out), t, inter, k, 1, self._wait_flag(), _stream()),
+            _check(self._core.sb_gemm_tcgen05(_p(h), _p(w_gate_up), _p(out), t, inter, k, 1, self._wait_flag(), self._s()),
                    "tcgen05 gate/up")
             return
         gate_up = torch.empty((t, 2 * inter), dtype=h.dtype, device=h.device)
@@ -198,7 +247,7 @@ class CudaKernels:
 
     def swiglu(self, gate_up, out) -> None:
         self.launches += 1
-        _check(self._core.sb_swiglu(_p(gate_up), _p(out), out.shape[0], out.shape[1], _DT[out.dtype], _stream()), "swiglu")
+        _check(self._core.sb_swiglu(_p(gate_up), _p(out), out.shape[0], out.shape[1], _DT[out.dtype], self._s()), "swiglu")
 
     def rope_cache_write(self, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
                          k_cache, v_cache, block_table, page_size, write_cache) -> None:
@@ -207,7 +256,7 @@ class CudaKernels:
         _check(self._core.sb_rope_cache_write(
             _p(qkv), _p(positions), _p(token_row), _p(inv_freq), pairing, rotary_dim, heads, kv_heads, head_dim,
             _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], page_size, num_pages,
-            1 if write_cache else 0, _p(self.errors_tensor()), qkv.shape[0], _DT[qkv.dtype], _stream()), "rope_cache_write")
+            1 if write_cache else 0, _p(self.errors_tensor()), qkv.shape[0], _DT[qkv.dtype], self._s()), "rope_cache_write")
 
     def qkv_rope_cache(self, h, w_qkv, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
                        k_cache, v_cache, block_table, page_size, write_cache) -> None:
@@ -224,7 +273,7 @@ class CudaKernels:
             _check(self._core.sb_skinny_qkv_rope(
                 _p(h), _p(w_qkv), _p(qkv), m, k, _p(positions), _p(token_row), _p(inv_freq), rotary_dim, heads, kv_heads, head_dim,
                 _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], page_size, k_cache.shape[0],
-                1 if write_cache else 0, _p(self.errors_tensor()), _stream()), "q/k/v product with rotation")
+                1 if write_cache else 0, _p(self.errors_tensor()), self._s()), "q/k/v product with rotation")
             return
         self.linear(h, w_qkv, qkv)
         self.rope_cache_write(qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
@@ -240,7 +289,7 @@ class CudaKernels:
         _check(lib.sb_attention_simt(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-            _DT[qkv.dtype], _stream()), "attention")
+            _DT[qkv.dtype], self._s()), "attention")
 
     # Thread blocks of the deep shape that fit the GPU at once (2 per SM): the key range of every request is
     # cut into so many splits that one wave of blocks covers the batch.
@@ -264,20 +313,26 @@ class CudaKernels:
             which |= 2
             if group > 8 or (shape.max_q > 1 and min(shape.max_q, 16 // group) * group > 8):
                 which |= 4      # some request of the deep shape may have more than 8 rows
+        # requests of the wide shape (more than 16 // group tokens): only they get blocks, if the step says who they are
+        wide_rows, n_wide = None, 0
+        neg_q = getattr(shape, "neg_q_sorted", None)
+        if (which & 1) and neg_q is not None and getattr(shape, "rows_by_q", None) is not None:
+            n_wide = bisect.bisect_left(neg_q, -(16 // group) if group <= 16 else 0)
+            wide_rows = shape.rows_by_q
         split_size, num_splits, scratch, tickets = 64, 1, None, None
         if which & 2:
             num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
             if num_splits > 1:
-                nbytes = lib.sb_attention_mma_scratch_bytes(shape.rows, kv_heads, num_splits)
-                scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
+                scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
-        if (which & 1) and self.use_tcgen05_attention and lib.sb_attention_tc_supports(heads, kv_heads, page_size, window, qkv.shape[1]):
+        if (which & 1) and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
             # prompt portions on the tensor-memory path; what is left (decoding rows) goes to the deep shape below
             self.launches += 1
             _check(lib.sb_attention_tc(
                 _p(qkv), qkv.shape[1], qkv.shape[0], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q),
-                _p(kv_len), heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), _p(out), shape.rows, shape.max_q,
-                self._wait_flag(), _stream()), "tcgen05 attention")
+                _p(kv_len), heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), _p(out),
+                n_wide if wide_rows is not None else shape.rows, shape.max_q, _p(wide_rows), self._wait_flag(), self._s()),
+                "tcgen05 attention")
             which &= ~1
             if not which:
                 return
@@ -285,7 +340,24 @@ class CudaKernels:
         _check(lib.sb_attention_mma(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-            which, split_size, num_splits, _p(scratch), _p(tickets), _stream()), "attention")
+            which, split_size, num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, self._s()), "attention")
+
+    def _tc_attention_takes(self, lib, heads, kv_heads, head_dim, page_size, window, stride) -> bool:
+        key = (heads, kv_heads, head_dim, page_size, window, stride)
+        ok = self._tc_attention_ok.get(key)
+        if ok is None:
+            ok = self._tc_attention_ok[key] = bool(lib.sb_attention_tc_supports(heads, kv_heads, page_size, window, stride))
+        return ok
+
+    def _scratch_buffer(self, lib, rows: int, kv_heads: int, num_splits: int) -> torch.Tensor:
+        """Float scratch for the partial results of split keys. Launches on one stream follow one another, so one buffer
+        serves all layers and steps; a larger one is made when needed and the old one stays alive for captured graphs."""
+        need = lib.sb_attention_mma_scratch_bytes(rows, kv_heads, num_splits) // 4
+        if self._split_scratch is None or self._split_scratch.numel() < need:
+            if self._split_scratch is not None:
+                self._keep.append(self._split_scratch)
+            self._split_scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=self.device)
+        return self._split_scratch
 
     def _ticket_buffer(self, n: int) -> torch.Tensor:
         """A zeroed int32 buffer of at least n entries. Every launch leaves it zeroed, so one buffer serves all
@@ -302,7 +374,7 @@ class CudaKernels:
             self._sample_work = torch.zeros(3 * max(n, 256), dtype=torch.int32, device=self.device)
             self._keep.append(self._sample_work)
         _check(self._core.sb_sample(_p(logits), _p(temperature), _p(req_ids), _p(tok_index), ctypes.c_ulonglong(seed),
-                                    n, logits.shape[1], _p(out), _p(self._sample_work), _p(slots), _p(last_token), _stream()),
+                                    n, logits.shape[1], _p(out), _p(self._sample_work), _p(slots), _p(last_token), self._s()),
                "sample")
 
 
