@@ -496,7 +496,8 @@ int pair_capacity(bool gate_up, int sms) {
 
 }  // namespace
 
-// Tests: 0 keeps every product on the one-CTA kernel, 1 (the default) sends tiles of more than 128 rows to CTA pairs.
+// 0 keeps every product on the one-CTA kernel, 1 (the default) lets products of more than 128 rows go to CTA pairs
+// where the tile plan says they are no slower, 2 sends all of those to CTA pairs (tests).
 SB_EXPORT void sb_gemm_tcgen05_use_pairs(int on) { g_pair_enabled = on; }
 SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(gate_up != 0, 148); }
 
@@ -521,20 +522,27 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  if (pair_mode(M)) {
-    // two CTAs per 256-row tile: as below, the width whose tiles need the least time in whole waves of CTA pairs
-    const long long m_tiles = (M + 255) / 256;
-    const int pairs = pair_capacity(gate_up != 0, sms);
-    int bn = BN;
-    if (!gate_up) {
-      long long best = -1;
-      for (int cand = BN; cand >= 128; cand -= 32) {
-        const long long n_tiles = (N + cand - 1) / cand;
-        const long long waves = (m_tiles * n_tiles + pairs - 1) / pairs;
-        const long long cost = waves * (cand + 32);
-        if (best < 0 || cost < best) { best = cost; bn = cand; }
-      }
+  // Tile plan. A wave of tiles takes about (tile width + a fixed part worth 32 columns) whether its tiles are 128 rows
+  // on one CTA or 256 rows on a CTA pair (each SM works on 128 rows either way), so the two kernels' costs compare
+  // directly: whole waves needed x that time, for the best width of each. Ragged row counts decide it: 330 rows are
+  // three 128-row tiles but two 256-row ones (512 rows of work).
+  const int widest = BN, narrowest = gate_up ? BN : 128;
+  long long cost_single = -1, cost_pair = -1;
+  int bn_single = BN, bn_pair = BN;
+  const int pairs = pair_mode(M) ? pair_capacity(gate_up != 0, sms) : 0;
+  for (int cand = widest; cand >= narrowest; cand -= 32) {
+    const int out_cols = gate_up ? cand / 2 : cand;
+    const long long n_tiles = (N + out_cols - 1) / out_cols;
+    const long long w1 = (((M + 127) / 128) * n_tiles + sms - 1) / sms;
+    if (cost_single < 0 || w1 * (cand + 32) < cost_single) { cost_single = w1 * (cand + 32); bn_single = cand; }
+    if (pairs > 0) {
+      const long long w2 = (((M + 255) / 256) * n_tiles + pairs - 1) / pairs;
+      if (cost_pair < 0 || w2 * (cand + 32) < cost_pair) { cost_pair = w2 * (cand + 32); bn_pair = cand; }
     }
+  }
+  if (pairs > 0 && (cost_pair <= cost_single || g_pair_enabled == 2)) {
+    const long long m_tiles = (M + 255) / 256;
+    const int bn = bn_pair;
     rc = make_map(&map_w, w, (uint64_t)(gate_up ? 2 * N : N), (uint64_t)K, bn / 2);
     if (rc) return rc;
     const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
@@ -547,16 +555,7 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
     return 0;
   }
   const long long m_tiles = (M + BM - 1) / BM;
-  int bn = BN;
-  if (!gate_up) {
-    long long best = -1;
-    for (int cand = BN; cand >= 128; cand -= 32) {
-      const long long n_tiles = (N + cand - 1) / cand;
-      const long long waves = (m_tiles * n_tiles + sms - 1) / sms;
-      const long long cost = waves * (cand + 32);
-      if (best < 0 || cost < best) { best = cost; bn = cand; }
-    }
-  }
+  const int bn = bn_single;
   rc = make_map(&map_w, w, (uint64_t)(gate_up ? 2 * N : N), (uint64_t)K, gate_up ? bn / 2 : bn);
   if (rc) return rc;
   const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 1024;

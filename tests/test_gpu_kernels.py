@@ -415,7 +415,7 @@ TC_SHAPES = [(128, 128, 64), (256, 256, 256), (2048, 3072, 2048), (300, 264, 200
 @pytest.fixture(params=["pairs", "single"])
 def cta_mode(K, request):
     """Tiles of more than 128 rows run on CTA pairs (cta_group::2) by default; "single" keeps them on the one-CTA kernel."""
-    K._core.sb_gemm_tcgen05_use_pairs(1 if request.param == "pairs" else 0)
+    K._core.sb_gemm_tcgen05_use_pairs(2 if request.param == "pairs" else 0)
     yield request.param
     K._core.sb_gemm_tcgen05_use_pairs(1)
 
