@@ -428,8 +428,10 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int G = p.G;
   const int M = qn * G;
-  if (M > 16 || M <= 0) return;                                 // the wide shape takes this request
-  if (UPPER != (M > 8)) return;                                 // the other instantiation takes this request
+  // A block with nothing to do still waits for the kernel before this one: the kernel after this one waits only for
+  // this one, so a launch whose blocks all left at once would let it run ahead of everything before.
+  if (M > 16 || M <= 0) { pdl_wait(); return; }                 // the wide shape takes this request
+  if (UPPER != (M > 8)) { pdl_wait(); return; }                 // the other instantiation takes this request
   const int L = p.kv_len[r];
   const int p0 = L - qn;
   int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;

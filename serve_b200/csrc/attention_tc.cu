@@ -152,10 +152,11 @@ __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_c
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int G = p.G;
   const int M = qn * G;
-  if (M <= 16) return;                                  // the deep shape takes this request
+  // (a block with nothing to do still waits for the kernel before this one: see attention_deep_kernel)
+  if (M <= 16) { pdl_wait(); return; }                  // the deep shape takes this request
   const int tok_per_tile = BM / G;
   const int n_mtiles = (qn + tok_per_tile - 1) / tok_per_tile;
-  if ((int)blockIdx.x >= n_mtiles) return;
+  if ((int)blockIdx.x >= n_mtiles) { pdl_wait(); return; }
   const int tile = n_mtiles - 1 - (int)blockIdx.x;      // later rows see more keys: they go first
   const int tok0 = tile * tok_per_tile;
   const int L = p.kv_len[r];
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_c
   int* bt_s = reinterpret_cast<int*>(base + TILE_BYTES + 256);
   if ((smem_u32(base) & 1023u) != 0) {                  // never seen; refuse rather than compute with a wrong swizzle
     if (threadIdx.x == 0) atomicExch(p.error, 1);
+    pdl_wait();
     return;
   }
 
@@ -209,6 +211,9 @@ __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // set up; queries, this step's keys and values, and the right to overwrite out come with the end of the kernel before
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t tmem_base = tmem_base_s;
   bool failed = false;
 
@@ -470,8 +475,7 @@ SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const
   const int m_tiles = (max_q + tok_per_tile - 1) / tok_per_tile;
   auto k = attention_tc_kernel;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  k<<<dim3(m_tiles, Hkv, n_rows), THREADS, SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
-  SB_LAUNCH_CHECK();
+  SB_PDL_CHECK(launch_pdl(k, dim3(m_tiles, Hkv, n_rows), dim3(THREADS), (size_t)SMEM_BYTES, stream, map_q, map_k, map_v, p));
   return 0;
 }
 

@@ -138,6 +138,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // barriers, tensor memory and descriptors are ready; the activations (and the right to overwrite out) come with
+  // the end of the kernel before this one
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t tmem_base = tmem_base_s;
   bool failed = false;
 
@@ -332,6 +336,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
   __syncthreads();
   cluster_sync_all_threads();            // the other CTA's barriers exist before anything arrives on them
   tc_fence_after();
+  pdl_launch_dependents();
+  pdl_wait();                            // as in the one-CTA kernel
   const uint32_t tmem_base = tmem_base_s;
   bool failed = false;
 
@@ -549,9 +555,10 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
     const int out_cols = gate_up ? bn / 2 : bn;
     const long long tiles = (long long)((N + out_cols - 1) / out_cols) * m_tiles;
     dim3 grid((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
-    if (gate_up) gemm_tcgen05_pair_kernel<true><<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
-    else gemm_tcgen05_pair_kernel<false><<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
-    SB_LAUNCH_CHECK();
+    if (gate_up)
+      SB_PDL_CHECK(launch_pdl(gemm_tcgen05_pair_kernel<true>, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
+    else
+      SB_PDL_CHECK(launch_pdl(gemm_tcgen05_pair_kernel<false>, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
     return 0;
   }
   const long long m_tiles = (M + BM - 1) / BM;
@@ -565,12 +572,11 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
   if (gate_up) {
     auto k = gemm_tcgen05_kernel<true>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
+    SB_PDL_CHECK(launch_pdl(k, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
   } else {
     auto k = gemm_tcgen05_kernel<false>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<grid, THREADS, smem, stream>>>(map_a, map_w, (bf16*)out, M, N, K, bn, error);
+    SB_PDL_CHECK(launch_pdl(k, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
   }
-  SB_LAUNCH_CHECK();
   return 0;
 }

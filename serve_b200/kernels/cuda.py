@@ -313,6 +313,11 @@ class CudaKernels:
             which |= 2
             if group > 8 or (shape.max_q > 1 and min(shape.max_q, 16 // group) * group > 8):
                 which |= 4      # some request of the deep shape may have more than 8 rows
+                neg_q = getattr(shape, "neg_q_sorted", None)
+                if neg_q is not None and group <= 8:
+                    # the step says how many tokens each request brings: is any count in (8 // group, 16 // group]?
+                    if bisect.bisect_left(neg_q, -(8 // group)) == bisect.bisect_left(neg_q, -(16 // group)):
+                        which &= ~4
         # requests of the wide shape (more than 16 // group tokens): only they get blocks, if the step says who they are
         wide_rows, n_wide = None, 0
         neg_q = getattr(shape, "neg_q_sorted", None)
