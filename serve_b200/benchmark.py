@@ -41,6 +41,9 @@ def main(argv=None) -> int:
     ap.add_argument("--output-length", type=int, default=256)
     ap.add_argument("--num-sequences", type=int, default=2000)
     ap.add_argument("--temperature", type=float, default=0.6)
+    # the load is 2000 requests at once: more live requests mean fewer, fuller steps (the reference admits up to 4000,
+    # serve/run.py:13)
+    ap.set_defaults(max_slots=1024)
     args = ap.parse_args(argv)
     engine = build_engine_from_args(args)
     reqs = generate_requests(args.input_length, args.output_length, args.num_sequences,
