@@ -1,4 +1,4 @@
-// Paged causal attention for prompt portions on the fifth-generation tensor cores (head_dim 64, bfloat16).
+// Paged causal attention for prompt portions on the fifth-generation tensor cores (head_dim 64 or 128, bfloat16).
 //
 // Work is cut as in attention_mma.cu: per (request, kv head), with the G = H / Hkv query heads that share the kv
 // head folded into the row dimension: row m stands for (token m / G, head hk*G + m % G). A CTA owns 128 such
@@ -17,7 +17,11 @@
 //              then, and only then, the accumulator in tensor memory is rescaled (tcgen05.ld / tcgen05.st) after
 //              the products issued so far have finished. So in the steady state nobody waits for the second
 //              product. At the end each thread divides its output row by the row's sum and stores 128 bytes.
-// Two CTAs share an SM (64 KB of shared memory, 256 columns of tensor memory each).
+// Two CTAs share an SM at head_dim 64 (96 KB of shared memory, 256 columns of tensor memory each).
+// At head_dim 128 an operand row is two 128-byte swizzle atoms: queries, keys and values arrive as two TMA boxes of 64
+// elements each, the first product walks over both atoms of Q and K, the second product covers the 128 output
+// columns in one instruction (the descriptor's leading byte offset names the distance between the atoms of V);
+// shared memory then holds one CTA per SM.
 // The recurrences are those of serve/kernels/attn_prefill.py:58-72 with exp2 and a folded log2(e)
 // (attn_prefill.py:330-331); probabilities are rounded to bfloat16 before the second product (attn_prefill.py:71).
 // Every wait is bounded; a wait that runs out raises *error and the CTA still frees its tensor memory.
@@ -25,14 +29,16 @@
 
 #include "common.cuh"
 
-#if SB_HEAD_DIM == 64
+#if SB_HEAD_DIM == 64 || SB_HEAD_DIM == 128
 
 using namespace sb;
 typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int D = 64;
+constexpr int D = SB_HEAD_DIM;
+constexpr int KA = D / 64;            // 128-byte swizzle atoms (64 elements) per operand row
+constexpr int CTAS_PER_SM = D == 64 ? 2 : 1;
 constexpr int BM = 128;              // rows per CTA
 constexpr int BN = 64;               // keys per tile (one 128-byte row of probabilities: one k-block of P)
 constexpr int NS = 3;                // key/value stages
@@ -42,7 +48,7 @@ constexpr uint32_t TMEM_COLS = 256;  // S0, S1 (BN columns each), O (64), rounde
 constexpr unsigned WAIT_LIMIT = 1u << 26;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int Q_BYTES = BM * D * 2, KV_BYTES = BN * D * 2, P_BYTES = BM * BN * 2;
-constexpr int TILE_BYTES = Q_BYTES + 2 * NS * KV_BYTES + 2 * P_BYTES;  // 96 KB
+constexpr int TILE_BYTES = Q_BYTES + 2 * NS * KV_BYTES + 2 * P_BYTES;  // 96 KB at head_dim 64, 160 KB at 128
 constexpr int SMEM_BYTES = TILE_BYTES + 256 + BT_CACHE * 4;             // + barriers + table entries; two CTAs fit an SM
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -145,7 +151,7 @@ struct TcParams {
   const int* rows;      // requests this launch covers (blockIdx.z indexes it); nullptr: all, in order
 };
 
-__global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(THREADS, CTAS_PER_SM) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v, const TcParams p) {
   const int r = p.rows ? p.rows[blockIdx.z] : (int)blockIdx.z, hk = blockIdx.y;
@@ -229,7 +235,8 @@ __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_c
     if (lane == 0) {
       // queries: box {64 elements, G heads, 1 kv head, tokens of the tile} -> rows (token, head)
       mbar_expect_tx(&q_full, (unsigned)(tok_per_tile * G * D * 2));
-      tma_load_4d(Qs, &map_q, &q_full, 0, 0, hk, q0 + tok0);
+#pragma unroll
+      for (int a = 0; a < KA; ++a) tma_load_4d(Qs + (size_t)a * BM * 128, &map_q, &q_full, a * 64, 0, hk, q0 + tok0);
       const int pages_per_tile = BN / p.ps;
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % NS;
@@ -241,8 +248,13 @@ __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_c
         mbar_expect_tx(&kv_full[s], (unsigned)(n_pages * p.ps * D * 2 * 2));
         for (int i = 0; i < n_pages; ++i) {
           const int page = bt[(kt + i * p.ps) / p.ps];
-          tma_load_4d(Ks + (size_t)s * KV_BYTES + (size_t)i * p.ps * D * 2, &map_k, &kv_full[s], 0, 0, hk, page);
-          tma_load_4d(Vs + (size_t)s * KV_BYTES + (size_t)i * p.ps * D * 2, &map_v, &kv_full[s], 0, 0, hk, page);
+#pragma unroll
+          for (int a = 0; a < KA; ++a) {
+            // atom a of a stage: 64 keys x 128 bytes; the page's keys at their rows of it
+            const size_t off = (size_t)s * KV_BYTES + (size_t)a * BN * 128 + (size_t)i * p.ps * 128;
+            tma_load_4d(Ks + off, &map_k, &kv_full[s], a * 64, 0, hk, page);
+            tma_load_4d(Vs + off, &map_v, &kv_full[s], a * 64, 0, hk, page);
+          }
         }
       }
     }
@@ -255,7 +267,12 @@ __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_c
         const uint64_t dk = make_desc(smem_u32(Ks + (size_t)(t % NS) * KV_BYTES), 0);
         const uint32_t acc = tmem_base + (uint32_t)((t & 1) * BN);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) tc_mma(acc, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk != 0 ? 1u : 0u);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          // 16 k-values further: 32 bytes within an atom (4 steps), then the next atom of Q (128 rows) and K (64 rows)
+          const uint64_t qo = (uint64_t)((kk >> 2) * (BM * 128 >> 4) + (kk & 3) * 2);
+          const uint64_t ko = (uint64_t)((kk >> 2) * (BN * 128 >> 4) + (kk & 3) * 2);
+          tc_mma(acc, dq + qo, dk + ko, idesc_s, kk != 0 ? 1u : 0u);
+        }
         tc_commit(&s_full[t & 1]);
       };
       do {
@@ -369,8 +386,11 @@ __global__ void __launch_bounds__(THREADS, 2) attention_tc_kernel(const __grid_c
         if (!mbar_wait(&kv_full[j % NS], (j / NS) & 1)) { failed = true; break; }
         unsigned char* vt = Vs + (size_t)(j % NS) * KV_BYTES;
         const int first = hi - kt;                       // rows [first, BN)
-        for (int idx = (warp - 2) * 32 + lane; idx < (BN - first) * 8; idx += 128)
-          *reinterpret_cast<uint4*>(vt + (size_t)(first + (idx >> 3)) * 128 + ((idx & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        for (int idx = (warp - 2) * 32 + lane; idx < (BN - first) * 8 * KA; idx += 128) {
+          const int a = idx / ((BN - first) * 8), rest = idx - a * (BN - first) * 8;
+          *reinterpret_cast<uint4*>(vt + (size_t)a * BN * 128 + (size_t)(first + (rest >> 3)) * 128 + ((rest & 7) << 4)) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
       }
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these writes are read by the tensor core
@@ -455,14 +475,14 @@ SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const
   {
     const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)G, (cuuint64_t)Hkv, (cuuint64_t)n_tokens};
     const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)G * D * 2, (cuuint64_t)q_stride * 2};
-    const cuuint32_t box[4] = {(cuuint32_t)D, (cuuint32_t)G, 1, (cuuint32_t)(BM / G)};
+    const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(BM / G)};   // one swizzle atom of the head
     int rc = encode4(&map_q, qkv, dims, strides, box);
     if (rc) return rc;
   }
   {
     const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, (cuuint64_t)num_pages};
     const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)ps * D * 2, (cuuint64_t)Hkv * ps * D * 2};
-    const cuuint32_t box[4] = {(cuuint32_t)D, (cuuint32_t)ps, 1, 1};
+    const cuuint32_t box[4] = {64, (cuuint32_t)ps, 1, 1};
     int rc = encode4(&map_k, kc, dims, strides, box);
     if (rc) return rc;
     rc = encode4(&map_v, vc, dims, strides, box);

@@ -501,12 +501,13 @@ TC_ATT_CASES = [
 ]
 
 
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("case", TC_ATT_CASES, ids=[f"h{c[0]}kv{c[1]}p{c[2]}n{len(c[3])}" for c in TC_ATT_CASES])
-def test_attention_tensor_memory_path(K, case):
-    """Prompt portions at head_dim 64 run on tcgen05 (TMA in, scores and output in tensor memory): against the
-    mma.sync kernel and the torch version, with unwritten cache rows poisoned."""
+def test_attention_tensor_memory_path(K, case, d):
+    """Prompt portions at head_dim 64 and 128 run on tcgen05 (TMA in, scores and output in tensor memory): against the
+    mma.sync kernel and the torch version, with unwritten cache rows poisoned. At 128 every operand row is two
+    swizzle atoms."""
     heads, kv_heads, page, q_lens, kv_lens = case
-    d = 64
     lib = K._attention_lib(d)
     assert lib.sb_attention_tc_supports(heads, kv_heads, page, 0, (heads + 2 * kv_heads) * d) == 1
     s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens, kv_lens)
@@ -535,10 +536,11 @@ def test_attention_tensor_memory_path(K, case):
     torch.testing.assert_close(outs["legacy"], outs["torch"], atol=2e-2, rtol=2e-2)
 
 
-def test_attention_tensor_memory_path_rescales_when_the_maximum_runs_ahead(K):
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_tensor_memory_path_rescales_when_the_maximum_runs_ahead(K, d):
     """The tcgen05 kernel keeps its output in tensor memory and rescales it only when a row's maximum has moved by
     more than a factor 2^8. Here later keys score far higher than earlier ones, several times in a row."""
-    heads, kv_heads, d, page = 4, 1, 64, 64
+    heads, kv_heads, page = 4, 1, 64
     L = 512
     s = _paged_setup("bfloat16", heads, kv_heads, d, page, [L], [L], seed=7)
     s["qkv"].mul_(0.1)

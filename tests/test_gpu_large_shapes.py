@@ -1,6 +1,8 @@
 """The engine at the benchmark's layer sizes (Llama-3.2-1B widths, two layers, a smaller vocabulary) against the plain
 implementation: only at these sizes do prompt portions run on the tcgen05 kernels (products with >= 96 tiles,
-attention at head_dim 64) and decoding on the fused few-rows kernels with their real widths."""
+attention at head_dim 64) and decoding on the fused few-rows kernels with their real widths. A second shape has the
+head size of the larger models (128: two swizzle atoms per operand row in the tcgen05 attention) and 3 query heads
+per key/value head."""
 import pytest
 import torch
 
@@ -14,15 +16,20 @@ CFG = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, num_hidden_laye
            rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                              original_max_position_embeddings=8192),
            tie_word_embeddings=True, max_position_embeddings=131072)
+CFG128 = dict(CFG, hidden_size=1536, num_attention_heads=12, num_key_value_heads=4, head_dim=128, intermediate_size=8192,
+              vocab_size=4096, tie_word_embeddings=False,
+              rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                original_max_position_embeddings=8192))
 
 
-@pytest.fixture(scope="module")
-def big(tmp_path_factory):
+@pytest.fixture(scope="module", params=["head_dim_64", "head_dim_128"])
+def big(tmp_path_factory, request):
     from serve_b200.config import config_from_dict
     from serve_b200.weights import write_random_model
 
     folder = str(tmp_path_factory.mktemp("big"))
-    write_random_model(folder, config_from_dict(CFG), seed=11, std=0.02, norm_std=0.05, dtype=torch.bfloat16)
+    cfg_dict = CFG if request.param == "head_dim_64" else CFG128
+    write_random_model(folder, config_from_dict(cfg_dict), seed=11, std=0.02, norm_std=0.05, dtype=torch.bfloat16)
     cfg, w = helpers.read_folder(folder)
     reqs = {"long": helpers.random_tokens(cfg["vocab_size"], 1600, seed=1), "short": helpers.random_tokens(cfg["vocab_size"], 300, seed=2)}
     with torch.no_grad():
