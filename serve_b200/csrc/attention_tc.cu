@@ -241,13 +241,13 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) attention_tc_kernel(cons
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % NS;
         if (!mbar_wait(&kv_empty[s], ((j / NS) & 1) ^ 1)) { failed = true; break; }
-        const int kt = j * BN;
+        const int kt = j * BN, blk0 = j * pages_per_tile;   // pages tile the stage: no division in this thread's loop
         int n_pages = 0;
         for (int i = 0; i < pages_per_tile; ++i)
-          if (kt + i * p.ps < hi && (kt + i * p.ps) / p.ps < p.bt_width) ++n_pages;
+          if (kt + i * p.ps < hi && blk0 + i < p.bt_width) ++n_pages;
         mbar_expect_tx(&kv_full[s], (unsigned)(n_pages * p.ps * D * 2 * 2));
         for (int i = 0; i < n_pages; ++i) {
-          const int page = bt[(kt + i * p.ps) / p.ps];
+          const int page = bt[blk0 + i];
 #pragma unroll
           for (int a = 0; a < KA; ++a) {
             // atom a of a stage: 64 keys x 128 bytes; the page's keys at their rows of it
