@@ -66,6 +66,7 @@ struct Params {
   const int* block_table; int bt_width;
   const int* cu_q; const int* kv_len;
   int H, Hkv, G, ps, num_pages;
+  int ps_shift;     // log2(ps) if ps is a power of two, else -1: a shift in place of a division in the key loops
   float scale_log2; int window;
   bf16* out;
   // deep shape only
@@ -382,7 +383,7 @@ constexpr int DCOPIES = DKW * CHUNKS / 32;                // 16-byte copies per 
 __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, int bt_first, int hk, int k0, int lo, int hi,
                                                 bool same_page, bf16* Ks, bf16* Vs, int lane) {
   if (same_page) {
-    const int blk = k0 / p.ps;
+    const int blk = p.ps_shift >= 0 ? (k0 >> p.ps_shift) : k0 / p.ps;
     const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
     const bool page_ok = page >= 0 && page < p.num_pages;
     const size_t base = (((size_t)(page_ok ? page : 0) * p.Hkv + hk) * p.ps + (k0 - blk * p.ps)) * D;
@@ -721,6 +722,7 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   p.qkv = (const bf16*)qkv; p.q_stride = q_stride; p.kc = (const bf16*)kc; p.vc = (const bf16*)vc;
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
+  p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
   p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = wide_rows;
@@ -806,6 +808,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.qkv = (const bf16*)qkv; p.q_stride = q_stride; p.kc = (const bf16*)kc; p.vc = (const bf16*)vc;
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
+  p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = nullptr;
