@@ -26,6 +26,24 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
   for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ok ? to_float(src[i]) : 0.f;
 }
 
+// A step's packed integer inputs, from pinned host memory to the device buffer the kernels read, copied by a kernel:
+// a few KB through the device's view of the host buffer. (As a memcpy the copy costs the same microseconds but sits
+// between two switches of engine, ~9 us of idle each, in a decoding step of under a millisecond.)
+__global__ void fetch_ints_kernel(const int4* __restrict__ src, int4* __restrict__ dst, int n4) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// src: pinned host memory (device-accessible), dst: device; n: ints, a multiple of 4; both 16-byte aligned.
+SB_EXPORT int sb_fetch_ints(const int* src, int* dst, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((n % 4) || !aligned16(src) || !aligned16(dst)) return SB_ERR_ALIGN;
+  const int n4 = n / 4;
+  const int blocks = n4 <= 1024 ? 1 : (n4 + 1023) / 1024 > 64 ? 64 : (n4 + 1023) / 1024;
+  fetch_ints_kernel<<<blocks, 256, 0, stream>>>((const int4*)src, (int4*)dst, n4);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
 SB_EXPORT int sb_embedding(const int* tokens, const void* table, float* out, int n_tokens, int dim, int vocab, int dtype,
                            const int* last_token, int n_slots, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;

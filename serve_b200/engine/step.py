@@ -236,7 +236,11 @@ class Stepper:
         for gi, (off, rr, w) in enumerate(lay.tables):
             rows = self.cache.table_rows(gi, rids, w)
             h[off: off + rr * w] = rows.reshape(-1)
-        dev[: lay.total].copy_(host[: lay.total], non_blocking=True)
+        fetch = getattr(self.rt.kernels, "fetch_ints", None) if self.on_cuda else None
+        if fetch is not None:
+            fetch(host, dev, lay.total)          # lay.total is a multiple of 4: every span is
+        else:
+            dev[: lay.total].copy_(host[: lay.total], non_blocking=True)
         self.last_h2d_bytes = lay.total * 4
         if self._events[self._turn] is not None:
             self._events[self._turn].record()

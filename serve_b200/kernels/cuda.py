@@ -174,6 +174,11 @@ class CudaKernels:
                 raise KernelError(f"{n} cache writes met a missing page or a block index beyond the block table")
 
     # ---- kernels ----------------------------------------------------------
+    def fetch_ints(self, host_pinned, dev, n: int) -> None:
+        """dev[:n] = host_pinned[:n] (int32, n a multiple of 4), copied by a kernel that reads the pinned host buffer."""
+        self.launches += 1
+        _check(self._core.sb_fetch_ints(_p(host_pinned), _p(dev), n, self._s()), "fetch of the step's inputs")
+
     def embedding(self, tokens, table, out, last_token=None) -> None:
         """out[t] = table[tokens[t]]; an id -(s+1) is replaced by last_token[s] (the token last sampled for slot s)."""
         self.launches += 1

@@ -130,17 +130,19 @@ def generate(model: Engine, requests: Sequence[Request], temperature: float = 0.
             sampling = [p.request for p in planned if p.samples]
             host = event = None
             if sampling:
-                out = sampler.sample(logits, [r.temperature for r in sampling], [r.rid for r in sampling],
-                                     [len(r.generated) for r in sampling], [model.cache.slot(r.rid) for r in sampling],
-                                     model.stepper.last_token)
                 turn ^= 1
                 if staging[turn] is None or staging[turn].numel() < len(sampling):
-                    staging[turn] = torch.empty(max(64, len(sampling)), dtype=torch.int32, pin_memory=on_cuda)
+                    staging[turn] = torch.empty(max(64, 1 << (len(sampling) - 1).bit_length()), dtype=torch.int32, pin_memory=on_cuda)
                 host = staging[turn]
-                host[: len(sampling)].copy_(out, non_blocking=True)
+                # on a GPU the sampling kernel writes the tokens straight into this pinned host buffer
+                out = sampler.sample(logits, [r.temperature for r in sampling], [r.rid for r in sampling],
+                                     [len(r.generated) for r in sampling], [model.cache.slot(r.rid) for r in sampling],
+                                     model.stepper.last_token, out=host if on_cuda else None)
                 if on_cuda:
                     event = torch.cuda.Event()
                     event.record()
+                else:
+                    host[: len(sampling)].copy_(out)
             n_dec = sum(1 for p in planned if len(p.tokens) == 1 and p.samples and p.request.generated)
             stamp = (sum(len(p.tokens) for p in planned) - n_dec, n_dec, model.stepper.last_h2d_bytes + 16 * len(sampling))
             idxs = [len(r.generated) for r in sampling]

@@ -26,8 +26,12 @@ class Sampler:
         self._event = None
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], request_ids: Sequence[int],
-               token_indices: Sequence[int], slots: Sequence[int] = None, last_token: torch.Tensor = None) -> torch.Tensor:
+               token_indices: Sequence[int], slots: Sequence[int] = None, last_token: torch.Tensor = None,
+               out: torch.Tensor = None) -> torch.Tensor:
         """logits [L, V] float32 -> int32 [L] on the device (one token per row).
+
+        ``out``, if given, receives the tokens instead of a new device tensor; it may be pinned host memory (the
+        kernel then writes the tokens straight to the host, and no copy back is needed once the kernel has ended).
 
         With ``slots`` and ``last_token`` the token of row r is also left in last_token[slots[r]] on the device, where
         the next step's embedding finds it (FROM_DEVICE) without a trip through the host."""
@@ -49,12 +53,19 @@ class Sampler:
         feed_back = slots is not None and last_token is not None
         if feed_back:
             h[3, :n] = slots
-        self._dev.copy_(self._host, non_blocking=True)
+        fetch = getattr(self.kernels, "fetch_ints", None) if self._pin else None
+        if fetch is not None:
+            fetch(self._host, self._dev, self._host.numel())
+        else:
+            self._dev.copy_(self._host, non_blocking=True)
         if self._pin:
             if self._event is None:
                 self._event = torch.cuda.Event()
             self._event.record()
-        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(n, dtype=torch.int32, device=self.device)
+        elif out.dtype != torch.int32 or out.numel() < n:
+            raise ValueError("out must hold one int32 per row of logits")
         self.kernels.sample(logits, self._dev[0, :n].view(torch.float32), self._dev[1, :n], self._dev[2, :n], self.seed, out,
                             self._dev[3, :n] if feed_back else None, last_token if feed_back else None)
         return out
