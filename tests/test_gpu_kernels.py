@@ -332,6 +332,32 @@ def test_attention_tensor_cores_against_plain_arithmetic(K, case):
     torch.testing.assert_close(outs["mma"], outs["torch"], atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,page,rows,max_q", [(32, 8, 64, 64, 150, 1), (16, 4, 128, 16, 300, 1), (24, 2, 64, 32, 520, 1),
+                                                               (8, 8, 64, 64, 140, 2), (12, 4, 32, 8, 260, 3)])
+def test_decode_attention_for_a_crowd_of_short_requests(K, heads, kv_heads, d, page, rows, max_q):
+    """A thousand and more (request, kv head) pairs in one step run one warp per pair. Short sequences of very
+    different lengths, one to three new tokens each, groups of 1, 3, 4 and 12 query heads; unwritten cache rows hold NaN."""
+    assert rows * kv_heads >= 1024
+    g = torch.Generator().manual_seed(rows)
+    q_lens = torch.randint(1, max_q + 1, (rows,), generator=g).tolist()
+    kv_lens = [q + int(x) for q, x in zip(q_lens, torch.randint(0, 330, (rows,), generator=g).tolist())]
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens, kv_lens)
+    for r, L in enumerate(kv_lens):
+        b = (L - 1) // page
+        if L % page:
+            s["kc"][int(s["bt"][r, b]), :, L % page:] = float("nan")
+            s["vc"][int(s["bt"][r, b]), :, L % page:] = float("nan")
+    t = sum(q_lens)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.full((t, heads * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ref = torch.empty_like(out)
+    K.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, 0, out, s["shape"])
+    K.check_errors()
+    E.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, 0, ref, s["shape"])
+    assert bool(torch.isfinite(out.float()).all()), "a row was not written, or NaN"
+    torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_attention_unwritten_cache_does_not_leak(K):
     """Pages hold NaN wherever nothing was written (beyond each request's length): outputs stay finite."""
     heads, kv_heads, d, page = 8, 2, 64, 16
