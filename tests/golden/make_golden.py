@@ -124,7 +124,9 @@ def run(name, M, KVIndex, page, n_tokens=24, prefill=5):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of limei1221/serve>")
+    ref = sys.argv[1]
     sys.path.insert(0, ref)
     sys.dont_write_bytecode = True
     import serve.model as M
