@@ -98,7 +98,8 @@ class Stepper:
         self._events: List[object] = [None, None]
         self._turn = 0
         self._dev: Optional[torch.Tensor] = None
-        self._graphs: Dict[tuple, object] = {}
+        self._graphs: Dict[tuple, object] = {}     # in order of last use
+        self._graph_pool = None                    # memory pool shared by all captured graphs
         self.launched_graphs = 0
         # the token last sampled for each state slot (written by the sampling kernel, read by the embedding)
         self.last_token = torch.zeros(cache.max_slots, dtype=torch.int32, device=runtime.device)
@@ -269,6 +270,13 @@ class Stepper:
         return logits
 
     # ---- CUDA graphs for pure-decode steps ------------------------------------
+    # Captured graphs kept; the least recently used goes. All graphs allocate from one shared pool (they never run at
+    # the same time), so a graph costs its nodes, not another copy of the activations.
+    MAX_GRAPHS = 1024
+
+    def _graph_key(self, r: int, longest: int):
+        return (r, min(self.cache.max_context, max(1024, 1 << (longest - 1).bit_length())))
+
     def _run_graph(self, ctx: StepContext, r: int, longest: int):
         """Replay (capturing on first use) the decode step for ``r`` requests.
 
@@ -278,10 +286,14 @@ class Stepper:
         batch's lengths, so one captured graph serves every decode step of that
         batch size until a sequence grows into the next class.
         """
-        bucket = min(self.cache.max_context, max(1024, 1 << (longest - 1).bit_length()))
-        key = (r, bucket)
-        g = self._graphs.get(key)
+        key = self._graph_key(r, longest)
+        bucket = key[1]
+        g = self._graphs.pop(key, None)
+        if g is not None:
+            self._graphs[key] = g              # most recently used last
         if g is None:
+            while len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
             shape = BatchShape(r, r, 1, 1, bucket, True)
             static_ctx = StepContext(**{**ctx.__dict__, "shape": shape})
             # warm up outside capture (allocator pools, cuBLAS workspaces, lazy module loads)
@@ -293,7 +305,9 @@ class Stepper:
             graph = torch.cuda.CUDAGraph()
             k = self.rt.kernels
             before = (getattr(k, "launches", 0), getattr(k, "library_calls", 0))
-            with torch.cuda.graph(graph), self._pinned_stream():
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool), self._pinned_stream():
                 out = self.model.forward(static_ctx, self.views)
             counts = (getattr(k, "launches", 0) - before[0], getattr(k, "library_calls", 0) - before[1])
             g = (graph, out, self._dev, counts)
