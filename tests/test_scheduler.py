@@ -117,3 +117,64 @@ def test_a_request_that_can_never_fit_is_refused():
     s.add(SchedRequest(3, [1] * 10, 3))                        # 12 tokens: exactly the pool
     run(s, cache)
     assert len(s.finished) == 1
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_loads_keep_every_promise(seed):
+    """Random requests, budgets, chunk sizes, pools and slot counts (pools small enough to force evictions): every
+    step stays under the token budget and the slot count, the pages it needs are there, nobody is fed a token twice
+    or out of order, requests are admitted in arrival order, and everybody ends with the tokens it asked for."""
+    import random
+
+    rng = random.Random(seed)
+    page = rng.choice([2, 4, 8])
+    n_req = rng.randint(3, 14)
+    reqs = [SchedRequest(i, [rng.randrange(100) for _ in range(rng.randint(1, 40))], rng.randint(1, 12)) for i in range(n_req)]
+    biggest = max(-(-(len(r.prompt) + r.max_new_tokens - 1) // page) for r in reqs)
+    num_pages = biggest + rng.randint(0, 2 * biggest)
+    slots = rng.randint(1, 6)
+    budget = rng.randint(2, 48)
+    chunk = rng.choice([None, rng.randint(1, 16)])
+    reserve_full = rng.random() < 0.3
+    cache = _cache(num_pages, page=page, slots=slots, ctx=64)
+    s = Scheduler(cache, max_tokens_per_step=budget, prefill_chunk=chunk, reserve_full=reserve_full)
+    for r in reqs:
+        s.add(r)
+    fed = {r.rid: [] for r in reqs}          # what the cache of each request holds, in order
+    first_seen = []
+    for _ in range(20_000):
+        if not s.has_work():
+            break
+        planned = s.plan()
+        for v in s.evicted:
+            cache.close(v.rid)
+            fed[v.rid] = []                  # recomputed from its prompt and what it had generated
+        assert planned
+        assert sum(len(p.tokens) for p in planned) <= budget
+        assert len({p.request.rid for p in planned}) == len(planned) <= slots
+        batch = []
+        for p in planned:
+            r = p.request
+            if r.rid not in first_seen:
+                first_seen.append(r.rid)
+            if not cache.is_open(r.rid):
+                cache.open(r.rid)
+            whole = r.prompt + [t for t in r.generated]
+            assert p.tokens == whole[len(fed[r.rid]): len(fed[r.rid]) + len(p.tokens)], "a token was skipped or fed twice"
+            assert p.samples == (len(fed[r.rid]) + len(p.tokens) == len(whole))
+            fed[r.rid] += p.tokens
+            batch.append((r.rid, len(fed[r.rid])))
+        cache.reserve(batch)                 # never raises: the scheduler counted the pages
+        for rid, n in batch:
+            cache.commit(rid, n)
+        cache.check()
+        done = s.update(planned, [rng.randrange(100) for p in planned if p.samples])
+        for r in done:
+            cache.close(r.rid)
+    assert not s.has_work(), "the scheduler did not finish"
+    assert first_seen == sorted(first_seen), "admission is in arrival order"
+    assert sorted(r.rid for r in s.finished) == list(range(n_req))
+    assert all(len(r.generated) == r.max_new_tokens for r in s.finished)
+    assert cache.live == 0 and all(g.pool.in_use == 0 for g in cache.groups)
+    if reserve_full:
+        assert s.stats.preemptions == 0
