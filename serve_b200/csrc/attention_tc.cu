@@ -5,7 +5,7 @@
 // rows (128 / G tokens) and walks over the request's keys in tiles of 64:
 //   warp 0     one thread feeds shared memory with TMA: the query tile once (a 4-d box over the q/k/v buffer),
 //              then per tile the key and value pages named by the block table (4-d boxes over the caches,
-//              128-byte swizzle), two stages;
+//              128-byte swizzle), three stages; the thread's loop is kept free of divisions, it is on the critical path;
 //   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 x 64 x 64) into one of two score buffers in tensor
 //              memory, and, once the probabilities of a tile are in shared memory, O += P V (128 x 64 x 64, V read
 //              MN-major) into the output accumulator, which stays in tensor memory for the whole walk;
@@ -16,7 +16,7 @@
 //              running maximum when that has moved by more than 8 (a factor 256, harmless in bfloat16 and float);
 //              then, and only then, the accumulator in tensor memory is rescaled (tcgen05.ld / tcgen05.st) after
 //              the products issued so far have finished. So in the steady state nobody waits for the second
-//              product. At the end each thread divides its output row by the row's sum and stores 128 bytes.
+//              product. At the end each thread divides its output row by the row's sum and stores its row.
 // Two CTAs share an SM at head_dim 64 (96 KB of shared memory, 256 columns of tensor memory each).
 // At head_dim 128 an operand row is two 128-byte swizzle atoms: queries, keys and values arrive as two TMA boxes of 64
 // elements each, the first product walks over both atoms of Q and K, the second product covers the 128 output
