@@ -632,16 +632,18 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   __syncthreads();                                              // every warp is done with its stages: reuse the memory
   float* Om = reinterpret_cast<float*>(smem_raw);               // [NWARPS][16][D]
   float* MLm = Om + NWARPS * 16 * D;                            // [NWARPS][16][2]
+  // only rows that exist are merged below: the others are not written
+  const bool row_a = g < M, row_b = UPPER && g + 8 < M;
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) {
     float* d0 = Om + ((size_t)warp * 16 + g) * D + i * 8 + tq * 2;
     float* d1 = Om + ((size_t)warp * 16 + g + 8) * D + i * 8 + tq * 2;
-    d0[0] = o[i][0]; d0[1] = o[i][1];
-    d1[0] = o[i][2]; d1[1] = o[i][3];
+    if (row_a) { d0[0] = o[i][0]; d0[1] = o[i][1]; }
+    if (row_b) { d1[0] = o[i][2]; d1[1] = o[i][3]; }
   }
   if (tq == 0) {
-    MLm[(warp * 16 + g) * 2] = m_a;      MLm[(warp * 16 + g) * 2 + 1] = l_a;
-    MLm[(warp * 16 + g + 8) * 2] = m_b;  MLm[(warp * 16 + g + 8) * 2 + 1] = l_b;
+    if (row_a) { MLm[(warp * 16 + g) * 2] = m_a; MLm[(warp * 16 + g) * 2 + 1] = l_a; }
+    if (row_b) { MLm[(warp * 16 + g + 8) * 2] = m_b; MLm[(warp * 16 + g + 8) * 2 + 1] = l_b; }
   }
   __syncthreads();
   const bool last = p.num_splits == 1;
