@@ -83,15 +83,31 @@ constexpr int MAX_SPLITS = 32;
 // Partial results of all key splits of (request r, kv head hk) -> the output rows. Reads bypass L1: the
 // partials were written by other SMs. First the (max, sum) pairs of all splits are fetched at once and turned
 // into one factor per (split, row); then every output element adds its S scaled partials, loads unrolled.
-// ``work``: (MAX_SPLITS + 1) * 16 floats of shared memory nobody else uses any more.
+// ``work``: (2 * MAX_SPLITS + 1) * 16 floats of shared memory nobody else uses any more.
 __device__ __forceinline__ void merge_splits(const Params& p, int r, int hk, int q0, int M, int nthreads, float* work) {
   float (*f_s)[16] = reinterpret_cast<float (*)[16]>(work);
   float* inv_s = work + MAX_SPLITS * 16;
+  float* l_s = inv_s + 16;                               // [S][16] sums, beside their maxima
   const int S = p.num_splits;
   const size_t base = ((size_t)r * p.Hkv + hk) * S;
+  // With few splits everything is asked for at once: the partial rows of this thread's first element go out together
+  // with the (max, sum) pairs, so the merge costs one trip to L2, not three one after the other (this code is the tail
+  // of the whole launch: the block that arrives last runs it alone).
+  constexpr int EARLY = 16;
+  const bool early = S <= EARLY && (int)threadIdx.x < M * D;
+  float v[EARLY];
+  if (early) {
+    const int row = threadIdx.x / D, d = threadIdx.x - row * D;
+#pragma unroll
+    for (int s_ = 0; s_ < EARLY; ++s_)
+      v[s_] = s_ < S ? __ldcg(p.part_o + ((base + s_) * 16 + row) * D + d) : 0.f;
+  }
   for (int idx = threadIdx.x; idx < S * 16; idx += nthreads) {
     const int s_ = idx >> 4, row = idx & 15;
-    f_s[s_][row] = row < M ? __ldcg(p.part_ml + ((base + s_) * 16 + row) * 2) : -INFINITY;
+    float2 ml = make_float2(-INFINITY, 0.f);
+    if (row < M) ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((base + s_) * 16 + row) * 2));
+    f_s[s_][row] = ml.x;
+    l_s[s_ * 16 + row] = ml.y;
   }
   __syncthreads();
   if (threadIdx.x < 16) {
@@ -102,7 +118,7 @@ __device__ __forceinline__ void merge_splits(const Params& p, int r, int hk, int
     for (int s_ = 0; s_ < S; ++s_) {
       const float ms = f_s[s_][row];
       const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-      if (f != 0.f) ll += __ldcg(p.part_ml + ((base + s_) * 16 + row) * 2 + 1) * f;
+      if (f != 0.f) ll += l_s[s_ * 16 + row] * f;
       f_s[s_][row] = f;
     }
     inv_s[row] = ll > 0.f ? 1.f / ll : 0.f;
@@ -111,22 +127,18 @@ __device__ __forceinline__ void merge_splits(const Params& p, int r, int hk, int
   for (int idx = threadIdx.x; idx < M * D; idx += nthreads) {
     const int row = idx / D, d = idx - row * D;
     float acc = 0.f;
-    int s_ = 0;
-    for (; s_ + 4 <= S; s_ += 4) {
-      const float v0 = __ldcg(p.part_o + ((base + s_) * 16 + row) * D + d);
-      const float v1 = __ldcg(p.part_o + ((base + s_ + 1) * 16 + row) * D + d);
-      const float v2 = __ldcg(p.part_o + ((base + s_ + 2) * 16 + row) * D + d);
-      const float v3 = __ldcg(p.part_o + ((base + s_ + 3) * 16 + row) * D + d);
+    if (early && idx == (int)threadIdx.x) {
       // a split without keys wrote no partial output: its factor is 0 and its (stale) values are not touched
-      const float f0 = f_s[s_][row], f1 = f_s[s_ + 1][row], f2 = f_s[s_ + 2][row], f3 = f_s[s_ + 3][row];
-      acc = f0 != 0.f ? fmaf(v0, f0, acc) : acc;
-      acc = f1 != 0.f ? fmaf(v1, f1, acc) : acc;
-      acc = f2 != 0.f ? fmaf(v2, f2, acc) : acc;
-      acc = f3 != 0.f ? fmaf(v3, f3, acc) : acc;
-    }
-    for (; s_ < S; ++s_) {
-      const float f = f_s[s_][row];
-      if (f != 0.f) acc = fmaf(__ldcg(p.part_o + ((base + s_) * 16 + row) * D + d), f, acc);
+#pragma unroll
+      for (int s_ = 0; s_ < EARLY; ++s_) {
+        const float f = s_ < S ? f_s[s_][row] : 0.f;
+        acc = f != 0.f ? fmaf(v[s_], f, acc) : acc;
+      }
+    } else {
+      for (int s_ = 0; s_ < S; ++s_) {
+        const float f = f_s[s_][row];
+        if (f != 0.f) acc = fmaf(__ldcg(p.part_o + ((base + s_) * 16 + row) * D + d), f, acc);
+      }
     }
     const int tok = row / p.G, hd = hk * p.G + (row - tok * p.G);
     p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(acc * inv_s[row]);
@@ -693,7 +705,7 @@ __global__ void __launch_bounds__(THREADS) attention_merge_kernel(const Params p
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int M = qn * p.G;
   if (M > 16 || M <= 0) return;
-  __shared__ float work[(MAX_SPLITS + 1) * 16];
+  __shared__ float work[(2 * MAX_SPLITS + 1) * 16];
   merge_splits(p, r, hk, q0, M, THREADS, work);
 }
 
