@@ -546,8 +546,10 @@ SB_EXPORT int sb_sample(const float* logits, const float* temperature, const int
   if (vocab <= 0 || !work) return SB_ERR_SHAPE;
   if (n_rows > 65535) return SB_ERR_LIMIT;
   const int threads = 256;
-  int chunks = (vocab + 4095) / 4096;      // at least 16 values per thread
-  if (chunks > 64) chunks = 64;
+  // few rows: more, smaller chunks, so that the launch still fills the GPU (at least 4 values per thread)
+  const int per_chunk = n_rows <= 16 ? 1024 : 4096;
+  int chunks = (vocab + per_chunk - 1) / per_chunk;
+  if (chunks > 128) chunks = 128;
   unsigned long long* keys = (unsigned long long*)work;
   int* counters = (int*)(keys + n_rows);
   SB_PDL_CHECK(launch_pdl(sample_kernel, dim3(n_rows, chunks), dim3(threads), 0, stream, logits, temperature, req_ids, tok_index,
