@@ -387,7 +387,7 @@ size_t wide_smem_bytes() { return (size_t)(64 + 2 * 2 * BN) * LDS * sizeof(bf16)
 // the mask; rows 8..15 of the tile are only computed when the request has that many (UPPER).
 constexpr int DKW = D <= 64 ? 32 : 16;                    // keys per warp per step
 constexpr int DNT = DKW / 8;                              // score n-tiles per step
-constexpr int DSTAGES = D <= 128 ? 3 : 2;                 // steps in flight per warp
+constexpr int DSTAGES = 2;                                 // steps in flight per warp
 constexpr bool DQ_IN_REGS = D <= 128;                     // query fragments live in registers
 constexpr int DCOPIES = DKW * CHUNKS / 32;                // 16-byte copies per lane per sub-tile and tensor
 
