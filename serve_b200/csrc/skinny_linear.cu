@@ -267,7 +267,13 @@ SB_EXPORT int sb_skinny_qkv_rope(const void* a, const void* w, void* out, int M,
   ra.positions = positions; ra.token_row = token_row; ra.inv_freq = inv_freq; ra.rot = rot; ra.H = H; ra.Hkv = Hkv; ra.D = D;
   ra.kc = (bf16*)kc; ra.vc = (bf16*)vc; ra.block_table = block_table; ra.bt_width = bt_width; ra.ps = ps; ra.num_pages = num_pages;
   ra.write_cache = write_cache; ra.errors = errors;
-  if (M <= 8) return launch<1, true, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+  if (M <= 8) {
+    // 8 columns a block would be more blocks than fit at once but fewer than two rounds of them (e.g. 384 for 296
+    // places): 16 columns a block then run in one round
+    const int blocks8 = (N + 7) / 8;
+    if (blocks8 > 296 && blocks8 <= 2 * 296) return launch<1, true, 2, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+    return launch<1, true, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+  }
   if (M <= 16) return launch<1, false, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
   return launch<2, false, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
 }
