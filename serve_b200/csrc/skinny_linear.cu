@@ -218,16 +218,26 @@ int launch(const void* a, const void* w, void* out, int M, int N, int K, const R
   return 0;
 }
 
+// Blocks of 8 columns (NT 1) or of 16 (NT 2)? Two blocks fit an SM. If 8-column blocks need more than one round of
+// them, 16-column blocks do the same work in fewer, fatter blocks (each pays its fixed part once): measured on the 1B
+// shapes, q/k/v (384 -> 192 blocks) and gate/up (1024 -> 512) gained 4 % of a decoding step each.
+inline bool wide_blocks(int N) {
+  int sms = 148;
+  return (N + 7) / 8 > 2 * sms;
+}
+
 template <bool GU, typename OutT>
 int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
   const RopeArgs none = {};
-  // more than ~8 blocks of 8 columns per SM: halve the block count, double the bytes each keeps in flight
-  const bool wide = !GU && N >= 148 * 8 * 8;
+  const bool wide = wide_blocks(N);
   if (M <= 8) {
     if (wide) return launch<1, true, 2, GU, false, OutT>(a, w, out, M, N, K, none, stream);
     return launch<1, true, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
   }
-  if (M <= 16 || GU) return launch<1, false, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
+  if (M <= 16 || GU) {
+    if (wide) return launch<1, false, 2, GU, false, OutT>(a, w, out, M, N, K, none, stream);
+    return launch<1, false, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
+  }
   return launch<2, false, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
 }
 
@@ -267,13 +277,14 @@ SB_EXPORT int sb_skinny_qkv_rope(const void* a, const void* w, void* out, int M,
   ra.positions = positions; ra.token_row = token_row; ra.inv_freq = inv_freq; ra.rot = rot; ra.H = H; ra.Hkv = Hkv; ra.D = D;
   ra.kc = (bf16*)kc; ra.vc = (bf16*)vc; ra.block_table = block_table; ra.bt_width = bt_width; ra.ps = ps; ra.num_pages = num_pages;
   ra.write_cache = write_cache; ra.errors = errors;
+  const bool wide = wide_blocks(N);
   if (M <= 8) {
-    // 8 columns a block would be more blocks than fit at once but fewer than two rounds of them (e.g. 384 for 296
-    // places): 16 columns a block then run in one round
-    const int blocks8 = (N + 7) / 8;
-    if (blocks8 > 296 && blocks8 <= 2 * 296) return launch<1, true, 2, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+    if (wide) return launch<1, true, 2, false, true, bf16>(a, w, out, M, N, K, ra, stream);
     return launch<1, true, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
   }
-  if (M <= 16) return launch<1, false, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+  if (M <= 16) {
+    if (wide) return launch<1, false, 2, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+    return launch<1, false, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
+  }
   return launch<2, false, 1, false, true, bf16>(a, w, out, M, N, K, ra, stream);
 }
