@@ -133,6 +133,33 @@ def decode_bench(eng, sampler, batch, steps, warmup, vocab, seed, cuda_profiler=
     return ms, ctx_mid, k.launches - l0, k.library_calls - c0
 
 
+def decode_timeline(eng, batch, vocab):
+    """One decoding step as it runs inside its graph: when each kernel starts (relative to the step's first kernel),
+    how long it runs, and how far its start lies before (-) or after (+) the end of everything launched before it.
+    With dependent launches a kernel's length includes the time it waits for its predecessor."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from serve_b200 import Request, generate
+
+    g = torch.Generator().manual_seed(1)
+    reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, 24) for _ in range(batch)]
+    generate(eng, reqs, temperature=0.0)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        generate(eng, reqs, temperature=0.0)
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+    firsts = [i for i, e in enumerate(evs) if "embedding" in e.name]
+    step = evs[firsts[-5]:firsts[-4]]
+    t0, prev_end = step[0].time_range.start, step[0].time_range.start
+    print(f"decoding step, batch {batch}: {evs[firsts[-4]].time_range.start - t0:.1f} us from first kernel to the next step's first kernel")
+    print(f"{'start us':>9} {'length us':>9} {'vs end of earlier':>17}  kernel")
+    for e in step:
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "")
+        print(f"{e.time_range.start - t0:9.2f} {e.time_range.end - e.time_range.start:9.2f} {e.time_range.start - prev_end:17.2f}  {name[:70]}")
+        prev_end = max(prev_end, e.time_range.end)
+    return 0
+
+
 def prefill_bench(eng, vocab, reps, seed, cuda_profiler=False):
     import torch
     from serve_b200.engine import StepEntry
@@ -215,7 +242,9 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for per-kernel profiles)")
     ap.add_argument("--cuda-profiler", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (ncu --profile-from-start off)")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None, help="measure just this part (for profiles)")
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline"], default=None,
+                    help="measure just this part (for profiles); timeline: start and length of every kernel of one decoding "
+                         "step as it runs inside its CUDA graph (torch.profiler), printed as a table")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (use --gpus 1)")
@@ -245,6 +274,8 @@ def main():
         sampler = Sampler(eng.kernels, eng.rt.device, seed=0)
         weights, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, 2)
 
+        if args.only == "timeline":
+            return decode_timeline(eng, args.batch, cfg.vocab_size)
         if args.only == "prefill":
             pre_ms = prefill_bench(eng, cfg.vocab_size, reps=2, seed=7, cuda_profiler=args.cuda_profiler)
             print(json.dumps({"only": "prefill", "ms": round(pre_ms, 3), "tokens": PREFILL_TOKENS}))
