@@ -160,6 +160,36 @@ def decode_timeline(eng, batch, vocab):
     return 0
 
 
+def prefill_timeline(eng, vocab):
+    """The kernels of one prompt step of PREFILL_TOKENS tokens, as decode_timeline prints them (first 40)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from serve_b200.engine import StepEntry
+
+    g = torch.Generator().manual_seed(3)
+    for rep in range(3):
+        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        if rep == 2:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                eng.step([StepEntry("tl", toks, [PREFILL_TOKENS - 1])])
+                torch.cuda.synchronize()
+        else:
+            eng.step([StepEntry("tl", toks, [PREFILL_TOKENS - 1])])
+        eng.end("tl")
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+    first = next(i for i, e in enumerate(evs) if "embedding" in e.name)
+    step = evs[first:]
+    t0, prev_end = step[0].time_range.start, step[0].time_range.start
+    print(f"prompt step of {PREFILL_TOKENS} tokens: {step[-1].time_range.end - t0:.1f} us from the first kernel's start to the last one's end")
+    print(f"{'start us':>9} {'length us':>9} {'vs end of earlier':>17}  kernel")
+    for e in step[:40]:
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "")
+        print(f"{e.time_range.start - t0:9.2f} {e.time_range.end - e.time_range.start:9.2f} {e.time_range.start - prev_end:17.2f}  {name[:70]}")
+        prev_end = max(prev_end, e.time_range.end)
+    return 0
+
+
 def prefill_bench(eng, vocab, reps, seed, cuda_profiler=False):
     import torch
     from serve_b200.engine import StepEntry
@@ -242,7 +272,7 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for per-kernel profiles)")
     ap.add_argument("--cuda-profiler", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (ncu --profile-from-start off)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "timeline-prefill"], default=None,
                     help="measure just this part (for profiles); timeline: start and length of every kernel of one decoding "
                          "step as it runs inside its CUDA graph (torch.profiler), printed as a table")
     args = ap.parse_args()
@@ -276,6 +306,8 @@ def main():
 
         if args.only == "timeline":
             return decode_timeline(eng, args.batch, cfg.vocab_size)
+        if args.only == "timeline-prefill":
+            return prefill_timeline(eng, cfg.vocab_size)
         if args.only == "prefill":
             pre_ms = prefill_bench(eng, cfg.vocab_size, reps=2, seed=7, cuda_profiler=args.cuda_profiler)
             print(json.dumps({"only": "prefill", "ms": round(pre_ms, 3), "tokens": PREFILL_TOKENS}))

@@ -447,6 +447,29 @@ SB_EXPORT int sb_rope_cache_write(void* qkv, const int* positions, const int* to
   return 0;
 }
 
+// (cos, sin) of position * inv_freq[j] for every rotary pair and every token of a step: float2 [half, n_tokens]
+// (pair-major: the threads of a warp that hold consecutive rows of a product read consecutive entries).
+// The angle is the float32 product that the rotary kernels form, so a value taken from here is the one they compute.
+__global__ void __launch_bounds__(256) rope_angles_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                                          int half, int n_tokens, float2* __restrict__ out) {
+  const long long total = (long long)n_tokens * half;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(idx / n_tokens), t = (int)(idx - (long long)j * n_tokens);
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+    out[idx] = make_float2(cs, sn);
+  }
+}
+
+SB_EXPORT int sb_rope_angles(const int* positions, const float* inv_freq, int rot, int n_tokens, float* out, cudaStream_t stream) {
+  if (n_tokens <= 0 || rot <= 0) return 0;
+  if ((rot & 1) || !positions || !inv_freq || !out || ((uintptr_t)out & 7)) return SB_ERR_SHAPE;
+  const long long total = (long long)n_tokens * (rot / 2);
+  const long long want = (total + 255) / 256;
+  rope_angles_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(positions, inv_freq, rot / 2, n_tokens, (float2*)out);
+  return (int)cudaGetLastError();
+}
+
 // ---------------------------------------------------------------- sampling
 // One block per row of float logits [L, V]. temperature 0: the largest logit,
 // lowest index on ties (serve/run.py:56-57). Otherwise the Gumbel-max form of

@@ -2,14 +2,16 @@
 // out[M,N] = a[M,K] * w[N,K]^T, bfloat16 in, float accumulation in tensor memory, bfloat16 out.
 // With gate_up, w is [2N, K] (gate rows, then up rows) and out[m,n] = silu(gate) * up (serve/model.py:85):
 // the activation is applied while the accumulator leaves tensor memory, and the [M, 2N] intermediate of the
-// unfused path is never written.
+// unfused path is never written. A third epilogue is the q/k/v product's (serve/model.py:120-124, 234-244): query and
+// key columns are rotated by their token's position, queries go to out, keys and values straight into the
+// request's cache pages, so the rotary kernel and its pass over q, k and v are not needed.
 //
 // A persistent CTA per SM walks over 128 x 256 tiles of the accumulator (with gate_up: 128 gate columns and
 // their 128 up columns, i.e. 128 output columns). Warp 0 feeds a ring of four shared-memory stages with TMA
 // (cp.async.bulk.tensor, 128-byte swizzle: one 128 x 64 box of a and a 256 x 64 box, or two 128 x 64 boxes, of
 // w per stage, completion counted on an mbarrier); one thread of warp 1 issues tcgen05.mma (128 x 256 x 16,
 // operands read from shared memory through matrix descriptors, accumulator in tensor memory) and releases
-// stages with tcgen05.commit; warps 2..5 read a finished accumulator back with tcgen05.ld, apply the epilogue
+// stages with tcgen05.commit; warps 2..17 read a finished accumulator back with tcgen05.ld, apply the epilogue
 // and store. Tensor memory holds two accumulators (2 x 256 columns), so the epilogue of one tile runs while
 // the products of the next are issued. Tiles that share a panel of w run at the same time on neighbouring
 // CTAs, so w comes from HBM once. Rows beyond M and k-values beyond K are zero-filled by TMA; stores are guarded.
@@ -27,7 +29,8 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64;      // accumulator tile and k-values per stage
 constexpr int NSTAGE = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int THREADS = 192;                     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
+constexpr int EPI_WARPS = 16;                    // two warps per quarter of the tensor-memory lanes: even and odd column chunks
+constexpr int THREADS = 64 + 32 * EPI_WARPS;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..9: epilogue
 constexpr unsigned WAIT_LIMIT = 1u << 26;
 constexpr uint32_t TMEM_COLS = 512;              // two accumulators of BN columns
 
@@ -94,10 +97,77 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-template <bool GU>
+constexpr int EPI_STORE = 0, EPI_GATE_UP = 1, EPI_ROPE = 2;
+
+// What the q/k/v epilogue needs: columns are [q heads | k heads | v heads] x D, D a multiple of 32 so that the 32
+// columns a thread holds at a time lie in one head. Adjacent pairs (2j, 2j+1) turn by position * inv_freq[j]; the
+// cosine and sine of that angle come from a table [rot/2, rows] made once per step (sb_rope_angles): an epilogue
+// warp has its scheduler to itself, so every instruction of a sincosf would be paid at full latency, 16 times per
+// 32 columns, and the epilogue, not the tensor core, would set the kernel's pace.
+struct RopeEpilogue {
+  const int* positions;
+  const int* token_row;
+  const float2* cos_sin;
+  const int* block_table;
+  bf16* kc;
+  bf16* vc;
+  int* errors;
+  int rot, H, Hkv, D, bt_width, ps, num_pages, write_cache;
+};
+
+// Where the keys and values of this thread's row go: element offset of (page, kv head 0, slot, 0) or -1.
+__device__ __forceinline__ long long rope_row_slot(const RopeEpilogue& ra, int row, int pos) {
+  const int blk = pos / ra.ps;
+  const int page = (blk < ra.bt_width && pos >= 0) ? ra.block_table[(size_t)ra.token_row[row] * ra.bt_width + blk] : -1;
+  if (page < 0 || page >= ra.num_pages) return -1;
+  return ((long long)page * ra.Hkv * ra.ps + (pos - blk * ra.ps)) * ra.D;
+}
+
+// 32 accumulator columns n .. n+31 of one row: rounded to bfloat16 as the unfused path stores them, q and k pairs
+// rotated, then q to out and k, v to the row's slot in the cache.
+__device__ __forceinline__ void rope_store_chunk(const RopeEpilogue& ra, const uint32_t (&v)[32], int row, int n, int M, int N,
+                                                 long long slot, bf16* __restrict__ out) {
+  const int head = n / ra.D, d0 = n - head * ra.D;
+  uint32_t packed[16];
+  const bool turns = head < ra.H + ra.Hkv;
+  // the table is [pair][row]: the 32 rows of a warp read 256 consecutive bytes per pair. All loads first, so that
+  // their latencies overlap (a warp alone on its scheduler has nothing else to run meanwhile).
+  float2 a[16];
+  const float2* angles = ra.cos_sin + (size_t)(d0 >> 1) * M + row;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) a[i] = (turns && d0 + 2 * i < ra.rot) ? __ldg(angles + (size_t)i * M) : make_float2(1.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float x = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i]))), y = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i + 1])));
+    __nv_bfloat162 o;
+    if (turns && d0 + 2 * i < ra.rot) o = __floats2bfloat162_rn(x * a[i].x - y * a[i].y, y * a[i].x + x * a[i].y);
+    else o = __floats2bfloat162_rn(x, y);
+    packed[i] = *reinterpret_cast<uint32_t*>(&o);
+  }
+  bf16* dst;
+  if (head < ra.H) {
+    dst = out + (size_t)row * N + n;
+  } else {
+    if (!ra.write_cache) return;
+    if (slot < 0) {
+      if (n == ra.H * ra.D) atomicAdd(ra.errors, 1);       // once per token
+      return;
+    }
+    const bool is_k = turns;
+    const int kvh = is_k ? head - ra.H : head - ra.H - ra.Hkv;
+    dst = (is_k ? ra.kc : ra.vc) + slot + (long long)kvh * ra.ps * ra.D + d0;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+}
+
+template <int EPI>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w, bf16* __restrict__ out,
-                                                               int M, int N, int K, int bn, int* __restrict__ error) {
+                                                               int M, int N, int K, int bn, int* __restrict__ error,
+                                                               const RopeEpilogue ra) {
+  constexpr bool GU = EPI == EPI_GATE_UP;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[NSTAGE];
   __shared__ __align__(8) uint64_t empty_bar[NSTAGE];
@@ -124,7 +194,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);       // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], EPI_WARPS);       // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -195,8 +265,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       }
     }
   } else {
-    // epilogue warps 2..5: a warp may touch the 32 tensor-memory lanes of its rank modulo 4
-    const int q = warp & 3;
+    // epilogue warps: a warp may touch the 32 tensor-memory lanes of its rank modulo 4; the warps of a quarter take
+    // the chunks of 32 columns in turn. With a tile or two per CTA the last tile's epilogue is not hidden behind any
+    // product, and a warp alone on its scheduler pays every instruction's latency in full: with four warps (one per
+    // quarter) the q/k/v product with rotation took 41.7 us inside a 2,048-token step, with eight 40.7, with sixteen 35.6.
+    const int q = warp & 3, c_first = ((warp - 2) >> 2) * 32;
     int local = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
@@ -205,11 +278,21 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+      int pos = 0;
+      long long slot = -1;
+      if (EPI == EPI_ROPE && row < M) {
+        pos = ra.positions[row];
+        if (ra.write_cache && n0 + OUT_COLS > ra.H * ra.D) slot = rope_row_slot(ra, row, pos);
+      }
 #pragma unroll 1
-      for (int c = 0; c < OUT_COLS; c += 32) {
+      for (int c = c_first; c < OUT_COLS; c += 32 * (EPI_WARPS / 4)) {
         if (n0 + c >= N) break;
         uint32_t v[32];
         tc_load32(acc + (uint32_t)c, v);
+        if (EPI == EPI_ROPE) {
+          if (row < M) rope_store_chunk(ra, v, row, n0 + c, M, N, slot, out);
+          continue;
+        }
         uint32_t packed[16];
         if (GU) {
           uint32_t u[32];
@@ -289,10 +372,12 @@ __device__ __forceinline__ void cluster_sync_all_threads() {
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
 
-template <bool GU>
+template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
     gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                             bf16* __restrict__ out, int M, int N, int K, int bn, int* __restrict__ error) {
+                             bf16* __restrict__ out, int M, int N, int K, int bn, int* __restrict__ error,
+                             const RopeEpilogue ra) {
+  constexpr bool GU = EPI == EPI_GATE_UP;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[PAIR_STAGES];
   __shared__ __align__(8) uint64_t empty_bar[PAIR_STAGES];
@@ -320,7 +405,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);       // one arrival per epilogue warp of both CTAs
+      mbar_init(&acc_empty[b], 2 * EPI_WARPS);   // one arrival per epilogue warp of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -384,7 +469,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3, c_first = ((warp - 2) >> 2) * 32;
     uint32_t leader_acc_empty[2];
 #pragma unroll
     for (int b = 0; b < 2; ++b)
@@ -397,11 +482,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+      int pos = 0;
+      long long slot = -1;
+      if (EPI == EPI_ROPE && row < M) {
+        pos = ra.positions[row];
+        if (ra.write_cache && n0 + OUT_COLS > ra.H * ra.D) slot = rope_row_slot(ra, row, pos);
+      }
 #pragma unroll 1
-      for (int c = 0; c < OUT_COLS; c += 32) {
+      for (int c = c_first; c < OUT_COLS; c += 32 * (EPI_WARPS / 4)) {
         if (n0 + c >= N) break;
         uint32_t v[32];
         tc_load32(acc + (uint32_t)c, v);
+        if (EPI == EPI_ROPE) {
+          if (row < M) rope_store_chunk(ra, v, row, n0 + c, M, N, slot, out);
+          continue;
+        }
         uint32_t packed[16];
         if (GU) {
           uint32_t u[32];
@@ -472,54 +567,59 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
 }
 
 int g_pair_enabled = 1;
-int g_pair_capacity[2] = {0, 0};
+int g_pair_capacity[3] = {0, 0, 0};
 
 bool pair_mode(int M) { return g_pair_enabled && M > 128; }
 
-// CTA pairs of the two-CTA kernel that the device holds at a time (the persistent grid's size)
-int pair_capacity(bool gate_up, int sms) {
-  int& cached = g_pair_capacity[gate_up ? 1 : 0];
-  if (cached > 0) return cached;
+template <int EPI>
+int pair_capacity_of(int sms) {
   const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(sms / 2 * 2, 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   int clusters = 0;
-  cudaError_t e;
-  if (gate_up) {
-    cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<true>, &cfg);
-  } else {
-    cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<false>, &cfg);
-  }
+  cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<EPI>, &cfg);
   if (e != cudaSuccess || clusters < 1) { cudaGetLastError(); clusters = sms / 2; }
-  if (clusters > sms / 2) clusters = sms / 2;
-  cached = clusters;
+  return clusters > sms / 2 ? sms / 2 : clusters;
+}
+
+// CTA pairs of the two-CTA kernel that the device holds at a time (the persistent grid's size)
+int pair_capacity(int epi, int sms) {
+  int& cached = g_pair_capacity[epi];
+  if (cached > 0) return cached;
+  cached = epi == EPI_GATE_UP ? pair_capacity_of<EPI_GATE_UP>(sms) : epi == EPI_ROPE ? pair_capacity_of<EPI_ROPE>(sms)
+                                                                                      : pair_capacity_of<EPI_STORE>(sms);
   return cached;
 }
 
-}  // namespace
+template <int EPI>
+cudaError_t launch_single(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_w, bf16* out,
+                          int M, int N, int K, int bn, int* error, const RopeEpilogue& ra) {
+  auto k = gemm_tcgen05_kernel<EPI>;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return launch_pdl(k, grid, dim3(THREADS), smem, stream, map_a, map_w, out, M, N, K, bn, error, ra);
+}
 
-// 0 keeps every product on the one-CTA kernel, 1 (the default) lets products of more than 128 rows go to CTA pairs
-// where the tile plan says they are no slower, 2 sends all of those to CTA pairs (tests).
-SB_EXPORT void sb_gemm_tcgen05_use_pairs(int on) { g_pair_enabled = on; }
-SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(gate_up != 0, 148); }
+template <int EPI>
+cudaError_t launch_pair(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_w, bf16* out,
+                        int M, int N, int K, int bn, int* error, const RopeEpilogue& ra) {
+  return launch_pdl(gemm_tcgen05_pair_kernel<EPI>, grid, dim3(THREADS), smem, stream, map_a, map_w, out, M, N, K, bn, error, ra);
+}
 
-// 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).
-SB_EXPORT int sb_gemm_tcgen05_supports(int M, int N, int K, int gate_up) {
+int supports(int M, int N, int K, int epi) {
   if (M < 1 || N < 8 || K < 8 || (K % 8) || (N % 8)) return 0;     // 16-byte row pitch for TMA, vector stores
-  if (gate_up && (N % 128)) return 0;                               // a tile's 128 gate rows must not reach into the up rows
+  if (epi == EPI_GATE_UP && (N % 128)) return 0;                    // a tile's 128 gate rows must not reach into the up rows
   return 1;
 }
 
-// a [M,K], w [N,K] (or [2N,K] with gate_up), out [M,N]; all bfloat16, row-major, 16-byte aligned.
-// error: device int set to 1 if a bounded wait inside the kernel ran out.
-SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int gate_up, int* error,
-                              cudaStream_t stream) {
-  if (!sb_gemm_tcgen05_supports(M, N, K, gate_up)) return SB_ERR_SHAPE;
+// a [M,K], w [N,K] (or [2N,K] with gate/up), out [M,N]; all bfloat16, row-major, 16-byte aligned.
+int run_product(const void* a, const void* w, void* out, int M, int N, int K, int epi, const RopeEpilogue& ra, int* error,
+                cudaStream_t stream) {
+  if (!supports(M, N, K, epi)) return SB_ERR_SHAPE;
   if (!aligned16(a) || !aligned16(w) || !aligned16(out) || !error) return SB_ERR_ALIGN;
+  const bool gate_up = epi == EPI_GATE_UP;
   CUtensorMap map_a, map_w;
   int rc = make_map(&map_a, a, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
@@ -535,7 +635,7 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
   const int widest = BN, narrowest = gate_up ? BN : 128;
   long long cost_single = -1, cost_pair = -1;
   int bn_single = BN, bn_pair = BN;
-  const int pairs = pair_mode(M) ? pair_capacity(gate_up != 0, sms) : 0;
+  const int pairs = pair_mode(M) ? pair_capacity(epi, sms) : 0;
   for (int cand = widest; cand >= narrowest; cand -= 32) {
     const int out_cols = gate_up ? cand / 2 : cand;
     const long long n_tiles = (N + out_cols - 1) / out_cols;
@@ -546,6 +646,7 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
       if (cost_pair < 0 || w2 * (cand + 32) < cost_pair) { cost_pair = w2 * (cand + 32); bn_pair = cand; }
     }
   }
+  cudaError_t e;
   if (pairs > 0 && (cost_pair <= cost_single || g_pair_enabled == 2)) {
     const long long m_tiles = (M + 255) / 256;
     const int bn = bn_pair;
@@ -555,10 +656,10 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
     const int out_cols = gate_up ? bn / 2 : bn;
     const long long tiles = (long long)((N + out_cols - 1) / out_cols) * m_tiles;
     dim3 grid((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
-    if (gate_up)
-      SB_PDL_CHECK(launch_pdl(gemm_tcgen05_pair_kernel<true>, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
-    else
-      SB_PDL_CHECK(launch_pdl(gemm_tcgen05_pair_kernel<false>, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
+    e = epi == EPI_GATE_UP ? launch_pair<EPI_GATE_UP>(grid, smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error, ra)
+        : epi == EPI_ROPE  ? launch_pair<EPI_ROPE>(grid, smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error, ra)
+                           : launch_pair<EPI_STORE>(grid, smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error, ra);
+    SB_PDL_CHECK(e);
     return 0;
   }
   const long long m_tiles = (M + BM - 1) / BM;
@@ -569,14 +670,54 @@ SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, in
   const int out_cols = gate_up ? bn / 2 : bn;
   const long long tiles = (long long)((N + out_cols - 1) / out_cols) * m_tiles;
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
-  if (gate_up) {
-    auto k = gemm_tcgen05_kernel<true>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    SB_PDL_CHECK(launch_pdl(k, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
-  } else {
-    auto k = gemm_tcgen05_kernel<false>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    SB_PDL_CHECK(launch_pdl(k, grid, dim3(THREADS), smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error));
-  }
+  e = epi == EPI_GATE_UP ? launch_single<EPI_GATE_UP>(grid, smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error, ra)
+      : epi == EPI_ROPE  ? launch_single<EPI_ROPE>(grid, smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error, ra)
+                         : launch_single<EPI_STORE>(grid, smem, stream, map_a, map_w, (bf16*)out, M, N, K, bn, error, ra);
+  SB_PDL_CHECK(e);
   return 0;
+}
+
+}  // namespace
+
+// 0 keeps every product on the one-CTA kernel, 1 (the default) lets products of more than 128 rows go to CTA pairs
+// where the tile plan says they are no slower, 2 sends all of those to CTA pairs (tests).
+SB_EXPORT void sb_gemm_tcgen05_use_pairs(int on) { g_pair_enabled = on; }
+SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(gate_up ? EPI_GATE_UP : EPI_STORE, 148); }
+
+// 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).
+SB_EXPORT int sb_gemm_tcgen05_supports(int M, int N, int K, int gate_up) { return supports(M, N, K, gate_up ? EPI_GATE_UP : EPI_STORE); }
+
+// error: device int set to 1 if a bounded wait inside the kernel ran out.
+SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int gate_up, int* error,
+                              cudaStream_t stream) {
+  return run_product(a, w, out, M, N, K, gate_up ? EPI_GATE_UP : EPI_STORE, RopeEpilogue{}, error, stream);
+}
+
+// 1 if sb_gemm_tcgen05_qkv_rope takes these sizes: whole heads of a multiple of 32 elements, an even rotary width.
+SB_EXPORT int sb_gemm_tcgen05_qkv_rope_supports(int M, int K, int rot, int H, int Hkv, int D) {
+  if (H < 1 || Hkv < 1 || D < 32 || (D % 32) || rot < 0 || rot > D || (rot & 1)) return 0;
+  return supports(M, (H + 2 * Hkv) * D, K, EPI_ROPE);
+}
+
+// The q/k/v product of an attention layer: out[M, (H + 2 Hkv) D] gets the rotated queries (its key and value columns
+// are left untouched); rotated keys and the values go to kc / vc [pages, Hkv, ps, D] at each token's position, through
+// its request's row of the block table. cos_sin [rot/2, M] pairs of floats from sb_rope_angles for the same positions. errors counts tokens without a page; wait_error as in sb_gemm_tcgen05.
+SB_EXPORT int sb_gemm_tcgen05_qkv_rope(const void* a, const void* w, void* out, int M, int K, const int* positions,
+                                       const int* token_row, const float* cos_sin, int rot, int H, int Hkv, int D, void* kc,
+                                       void* vc, const int* block_table, int bt_width, int ps, int num_pages, int write_cache,
+                                       int* errors, int* wait_error, cudaStream_t stream) {
+  if (!sb_gemm_tcgen05_qkv_rope_supports(M, K, rot, H, Hkv, D) || ps <= 0) return SB_ERR_SHAPE;
+  if (!positions || !errors || (rot > 0 && (!cos_sin || ((uintptr_t)cos_sin & 7)))) return SB_ERR_ALIGN;
+  if (write_cache && (!kc || !vc || !block_table || !token_row || !aligned16(kc) || !aligned16(vc))) return SB_ERR_ALIGN;
+  RopeEpilogue ra;
+  ra.positions = positions;
+  ra.token_row = token_row;
+  ra.cos_sin = (const float2*)cos_sin;
+  ra.block_table = block_table;
+  ra.kc = (bf16*)kc;
+  ra.vc = (bf16*)vc;
+  ra.errors = errors;
+  ra.rot = rot; ra.H = H; ra.Hkv = Hkv; ra.D = D;
+  ra.bt_width = bt_width; ra.ps = ps; ra.num_pages = num_pages; ra.write_cache = write_cache;
+  return run_product(a, w, out, M, (H + 2 * Hkv) * D, K, EPI_ROPE, ra, wait_error, stream);
 }

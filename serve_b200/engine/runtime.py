@@ -19,6 +19,7 @@ class Runtime:
         self.kernels = kernels
         self.device = torch.device(device)
         self.act_dtype = act_dtype
+        self.constants = {}      # device tensors that parts with equal parameters share (keyed by those parameters)
 
     @classmethod
     def describe_only(cls) -> "Runtime":

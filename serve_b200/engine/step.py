@@ -61,6 +61,8 @@ class StepContext:
     block_tables: List[torch.Tensor]   # per cache group: [R, W] int32
     rids: List[Hashable] = field(default_factory=list)
     last_token: Optional[torch.Tensor] = None   # [max_slots] int32: the token last sampled for each state slot
+    memo: Dict[Hashable, object] = field(default_factory=dict)   # what a part derives from the step's arrays alone
+    #                                                               (one layer makes it, the layers after it find it)
 
 
 def _align4(n: int) -> int:

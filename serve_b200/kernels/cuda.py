@@ -264,12 +264,13 @@ class CudaKernels:
             1 if write_cache else 0, _p(self.errors_tensor()), qkv.shape[0], _DT[qkv.dtype], self._s()), "rope_cache_write")
 
     def qkv_rope_cache(self, h, w_qkv, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
-                       k_cache, v_cache, block_table, page_size, write_cache) -> None:
+                       k_cache, v_cache, block_table, page_size, write_cache, memo=None) -> None:
         """qkv = h @ w_qkv^T, queries and keys rotated, keys and values written to the cache pages.
 
-        For a handful of rows, bfloat16 and adjacent rotary pairs this is one kernel (the product with rotation and
-        cache write in its epilogue; only the query columns of ``qkv`` are then written). Otherwise the product and
-        the rotary kernel run one after the other."""
+        In bfloat16 with adjacent rotary pairs this is one kernel, for a handful of rows and for many (the product with
+        rotation and cache write in its epilogue; only the query columns of ``qkv`` are then written). Otherwise, and
+        for row counts in between that go to the library, the product and the rotary kernel run one after the other.
+        ``memo``: a dict that lives as long as the step's positions do; what depends on them alone is kept there."""
         m, k = h.shape
         n = qkv.shape[1]
         if (h.dtype == torch.bfloat16 and self.use_skinny_linear and self.fuse_rope and pairing == 1 and head_dim % 8 == 0
@@ -279,6 +280,26 @@ class CudaKernels:
                 _p(h), _p(w_qkv), _p(qkv), m, k, _p(positions), _p(token_row), _p(inv_freq), rotary_dim, heads, kv_heads, head_dim,
                 _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], page_size, k_cache.shape[0],
                 1 if write_cache else 0, _p(self.errors_tensor()), self._s()), "q/k/v product with rotation")
+            return
+        if (h.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16 and self.fuse_rope and pairing == 1
+                and self._tcgen05_worthwhile(m, n)
+                and self._core.sb_gemm_tcgen05_qkv_rope_supports(m, k, rotary_dim, heads, kv_heads, head_dim)):
+            # many rows: the tensor-memory product with the same epilogue; cosines and sines from a table that the
+            # first layer of the step makes and the others find in the step's memo
+            key = ("rope_angles", inv_freq.data_ptr(), positions.data_ptr(), rotary_dim)
+            angles = memo.get(key) if memo is not None else None
+            if angles is None:
+                angles = torch.empty((max(rotary_dim // 2, 1), m, 2), dtype=torch.float32, device=h.device)
+                self.launches += 1
+                _check(self._core.sb_rope_angles(_p(positions), _p(inv_freq), rotary_dim, m, _p(angles), self._s()), "rotary angles")
+                if memo is not None:
+                    memo[key] = angles
+            self.launches += 1
+            _check(self._core.sb_gemm_tcgen05_qkv_rope(
+                _p(h), _p(w_qkv), _p(qkv), m, k, _p(positions), _p(token_row), _p(angles), rotary_dim, heads, kv_heads, head_dim,
+                _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], page_size, k_cache.shape[0],
+                1 if write_cache else 0, _p(self.errors_tensor()), self._wait_flag(), self._s()),
+                "tcgen05 q/k/v product with rotation")
             return
         self.linear(h, w_qkv, qkv)
         self.rope_cache_write(qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,

@@ -91,7 +91,7 @@ class Attention(Mixer):
         rt.kernels.qkv_rope_cache(
             h, self.w_qkv, qkv, ctx.positions, ctx.token_row, self.position.inv_freq, self.pairing,
             self.position.rotary_dim, self.heads, self.kv_heads, self.head_dim,
-            cache.k, cache.v, block_table, cache.page_size, cache.writes,
+            cache.k, cache.v, block_table, cache.page_size, cache.writes, memo=getattr(ctx, "memo", None),
         )
         attn = rt.empty_act((t, self.q_size))
         rt.kernels.attention(

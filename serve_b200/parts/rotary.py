@@ -64,7 +64,15 @@ class Rotary(PositionEncoding):
         if pairing not in ("half", "interleaved"):
             raise ValueError(f"rotary pairing {pairing!r} is not known (half, interleaved)")
         self.pairing = PAIRING_HALF if pairing == "half" else PAIRING_INTERLEAVED
-        self.inv_freq = rotary_inv_freq(self.rotary_dim, self.theta, self.scaling).to(runtime.device)
+        # layers with the same frequencies share one tensor: what a step derives from it is then made once, not per layer
+        key = ("rotary_inv_freq", self.rotary_dim, self.theta, tuple(sorted(self.scaling.items())) if self.scaling else None)
+        constants = getattr(runtime, "constants", None)
+        if constants is None or key not in constants:
+            made = rotary_inv_freq(self.rotary_dim, self.theta, self.scaling).to(runtime.device)
+            if constants is None:
+                constants = {}
+            constants[key] = made
+        self.inv_freq = constants[key]
 
 
 @register_part("position", "none")

@@ -62,7 +62,7 @@ class EmuKernels:
         self.swiglu(gate_up, out)
 
     def qkv_rope_cache(self, h, w_qkv, qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
-                       k_cache, v_cache, block_table, page_size, write_cache):
+                       k_cache, v_cache, block_table, page_size, write_cache, memo=None):
         self.linear(h, w_qkv, qkv)
         self.rope_cache_write(qkv, positions, token_row, inv_freq, pairing, rotary_dim, heads, kv_heads, head_dim,
                               k_cache, v_cache, block_table, page_size, write_cache)

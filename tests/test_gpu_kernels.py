@@ -504,10 +504,75 @@ def test_tcgen05_gate_up_with_swiglu(K, m, inter, k, cta_mode):
     torch.testing.assert_close(fused.float(), ref.float(), atol=scale * 2.0 ** -6, rtol=0)
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,rot,page,k,q_lens,kv_lens", [
+    (8, 2, 64, 64, 64, 512, [300, 1, 129], [300, 33, 400]),        # whole tiles and a ragged last one
+    (5, 1, 96, 64, 16, 200, [70, 200], [70, 333]),                 # partial rotation, 3 chunks of 32 a head, ragged k
+    (3, 3, 128, 128, 8, 136, [257], [1000]),                       # as many k/v heads as q heads, tiny pages
+    (2, 1, 32, 32, 32, 64, [64], [64])])                           # a tile wider than all the columns
+def test_tcgen05_qkv_product_with_rotation(K, heads, kv_heads, d, rot, page, k, q_lens, kv_lens, cta_mode):
+    """The q/k/v product whose epilogue rotates and writes the cache against the product followed by the rotary kernel:
+    same rounding points, so they agree to the last bit of bfloat16 except where the compiler contracted differently."""
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens=q_lens, kv_lens=kv_lens, seed=5)
+    t, n = s["qkv"].shape
+    h = torch.randn(t, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    inv = (1.0 / (500000.0 ** (torch.arange(0, rot, 2).float() / rot))).to(DEV)
+    assert K._core.sb_gemm_tcgen05_qkv_rope_supports(t, k, rot, heads, kv_heads, d) == 1
+    a = {key: (v.clone() if torch.is_tensor(v) else v) for key, v in s.items()}
+    b = {key: (v.clone() if torch.is_tensor(v) else v) for key, v in s.items()}
+    a["qkv"].fill_(float("nan"))
+    K.TCGEN05_MIN_TILES = 1
+    try:
+        before = K.launches
+        memo = {}
+        K.qkv_rope_cache(h, w, a["qkv"], a["pos"], a["row"], inv, 1, rot, heads, kv_heads, d, a["kc"], a["vc"], a["bt"], page, True,
+                         memo=memo)
+        assert K.launches == before + 2, "the step's table of cosines and sines, and one kernel for the rest"
+        # a later layer of the step finds the table; one that reads another layer's cache rotates its queries and
+        # writes no page
+        c = {key: (v.clone() if torch.is_tensor(v) else v) for key, v in s.items()}
+        K.qkv_rope_cache(h, w, c["qkv"], a["pos"], c["row"], inv, 1, rot, heads, kv_heads, d, c["kc"], c["vc"], c["bt"], page, False,
+                         memo=memo)
+        assert K.launches == before + 3
+        K.fuse_rope = False
+        K.qkv_rope_cache(h, w, b["qkv"], b["pos"], b["row"], inv, 1, rot, heads, kv_heads, d, b["kc"], b["vc"], b["bt"], page, True)
+        assert K.launches == before + 5
+    finally:
+        K.fuse_rope = True
+        K.TCGEN05_MIN_TILES = type(K).TCGEN05_MIN_TILES
+    K.check_errors()
+    q_cols = heads * d
+    assert bool(torch.isfinite(a["qkv"][:, :q_cols].float()).all()), "a query tile was not written"
+    ulp = dict(atol=2.0 ** -7 * float(b["qkv"][:, :q_cols].float().abs().max()), rtol=0)
+    torch.testing.assert_close(a["qkv"][:, :q_cols].float(), b["qkv"][:, :q_cols].float(), **ulp)
+    torch.testing.assert_close(a["kc"].float(), b["kc"].float(), **ulp)
+    assert torch.equal(a["vc"], b["vc"])
+    assert not torch.equal(a["kc"], s["kc"]) and not torch.equal(a["vc"], s["vc"])
+    assert torch.equal(c["kc"], s["kc"]) and torch.equal(c["vc"], s["vc"])
+    assert torch.equal(c["qkv"][:, :q_cols], a["qkv"][:, :q_cols])
+    # against float64 from the definition: the product, then pairs (2j, 2j+1) turned by position * inv_freq[j]
+    full = (h.double() @ w.double().T).view(t, heads + 2 * kv_heads, d)
+    ang = s["pos"].double()[:, None] * inv.double()[None]
+    x, y = full[:, :heads + kv_heads, 0:rot:2], full[:, :heads + kv_heads, 1:rot:2]
+    turned = full.clone()
+    turned[:, :heads + kv_heads, 0:rot:2] = x * ang.cos()[:, None] - y * ang.sin()[:, None]
+    turned[:, :heads + kv_heads, 1:rot:2] = y * ang.cos()[:, None] + x * ang.sin()[:, None]
+    tol = dict(atol=float(turned.abs().max()) * 2.0 ** -6, rtol=0)
+    torch.testing.assert_close(a["qkv"][:, :q_cols].double().view(t, heads, d), turned[:, :heads], **tol)
+    pos, row = s["pos"].long(), s["row"].long()
+    pages = s["bt"].long()[row, pos // page]
+    got_k = a["kc"][pages, :, pos % page].double()            # [t, kv_heads, d]
+    got_v = a["vc"][pages, :, pos % page].double()
+    torch.testing.assert_close(got_k, turned[:, heads:heads + kv_heads], **tol)
+    torch.testing.assert_close(got_v, turned[:, heads + kv_heads:], **tol)
+
+
 def test_sizes_the_tcgen05_product_leaves_to_the_library(K):
     assert K._core.sb_gemm_tcgen05_supports(128, 100, 64, 0) == 0      # output rows must be 16-byte multiples
     assert K._core.sb_gemm_tcgen05_supports(128, 128, 60, 0) == 0      # so must input rows (TMA pitch)
     assert K._core.sb_gemm_tcgen05_supports(128, 192, 64, 1) == 0      # gate tile would reach into the up rows
+    assert K._core.sb_gemm_tcgen05_qkv_rope_supports(128, 64, 48, 4, 2, 48) == 0   # heads of 48: a 32-column chunk would span two
+    assert K._core.sb_gemm_tcgen05_qkv_rope_supports(128, 64, 31, 4, 2, 64) == 0   # pairs need an even rotary width
     a = torch.randn(128, 60, device=DEV).to(torch.bfloat16)
     w = torch.randn(100, 60, device=DEV).to(torch.bfloat16)
     out = torch.empty(128, 100, device=DEV, dtype=torch.bfloat16)
