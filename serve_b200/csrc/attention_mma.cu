@@ -76,6 +76,7 @@ struct Params {
   int* tickets;     // [R, Hkv] zero before the launch and again after it; nullptr: a separate kernel merges
   // wide shape only
   const int* wide_rows;   // requests the launch covers (blockIdx.z indexes it); nullptr: all, in order
+  int heads_in_x;         // wide shape: grid (kv heads, row tiles, requests) rather than (row tiles, kv heads, requests)
 };
 
 constexpr int MAX_SPLITS = 32;
@@ -206,14 +207,16 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [BM][LDS]
   bf16* KVs = Qs + BM * LDS;                        // 2 stages x (K [BN][LDS], V [BN][LDS])
 
-  const int r = p.wide_rows ? p.wide_rows[blockIdx.z] : (int)blockIdx.z, hk = blockIdx.y;
+  // blocks start in the order of blockIdx.x, then y: with the heads in x the longest tiles of all heads start first
+  const int r = p.wide_rows ? p.wide_rows[blockIdx.z] : (int)blockIdx.z;
+  const int hk = p.heads_in_x ? blockIdx.x : blockIdx.y, bx = p.heads_in_x ? blockIdx.y : blockIdx.x;
   const int q0 = p.cu_q[r], qn = p.cu_q[r + 1] - q0;
   const int G = p.G;
   const int M = qn * G;                             // rows of this (request, kv head)
   if (M <= 16) return;                              // the deep shape takes this request
   const int n_mtiles = (M + BM - 1) / BM;
-  if ((int)blockIdx.x >= n_mtiles) return;
-  const int m0 = (n_mtiles - 1 - (int)blockIdx.x) * BM;   // later rows see more keys: they go first
+  if (bx >= n_mtiles) return;
+  const int m0 = (n_mtiles - 1 - bx) * BM;          // later rows see more keys: they go first
   const int L = p.kv_len[r];
   const int p0 = L - qn;                            // position of the request's first query
   const int tok_first = m0 / G, row_last = min(m0 + BM, M) - 1;
@@ -739,7 +742,7 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
   p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
-  p.wide_rows = wide_rows;
+  p.wide_rows = wide_rows; p.heads_in_x = 0;
   if (which & 1) {
     auto k = attention_wide_kernel;
     const size_t smem = wide_smem_bytes();
@@ -747,7 +750,8 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
     const long long tiles = ((long long)max_q * p.G + 63) / 64;
     if (tiles > 2147483647LL) return SB_ERR_LIMIT;
     const int z = wide_rows ? n_wide : n_rows;
-    if (z > 0) k<<<dim3((unsigned)tiles, Hkv, z), THREADS, smem, stream>>>(p);
+    p.heads_in_x = tiles <= 65535 ? 1 : 0;
+    if (z > 0) k<<<p.heads_in_x ? dim3(Hkv, (unsigned)tiles, z) : dim3((unsigned)tiles, Hkv, z), THREADS, smem, stream>>>(p);
     SB_LAUNCH_CHECK();
   }
   if (which & 2) {
