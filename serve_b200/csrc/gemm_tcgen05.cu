@@ -567,6 +567,7 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
 }
 
 int g_pair_enabled = 1;
+int g_forced_width = 0;      // tests: accumulator columns per tile instead of the tile plan's choice
 int g_pair_capacity[3] = {0, 0, 0};
 
 bool pair_mode(int M) { return g_pair_enabled && M > 128; }
@@ -632,8 +633,9 @@ int run_product(const void* a, const void* w, void* out, int M, int N, int K, in
   // on one CTA or 256 rows on a CTA pair (each SM works on 128 rows either way), so the two kernels' costs compare
   // directly: whole waves needed x that time, for the best width of each. Ragged row counts decide it: 330 rows are
   // three 128-row tiles but two 256-row ones (512 rows of work).
-  const int widest = BN, narrowest = gate_up ? BN : 128;
-  long long cost_single = -1, cost_pair = -1;
+  const bool forced = g_forced_width >= 32 && g_forced_width <= BN && (g_forced_width % 32) == 0 && !gate_up;
+  const int widest = forced ? g_forced_width : BN, narrowest = forced ? g_forced_width : (gate_up ? BN : 128);
+  long long cost_single = -1, cost_pair = -1, waves_pair = 0;
   int bn_single = BN, bn_pair = BN;
   const int pairs = pair_mode(M) ? pair_capacity(epi, sms) : 0;
   for (int cand = widest; cand >= narrowest; cand -= 32) {
@@ -643,11 +645,16 @@ int run_product(const void* a, const void* w, void* out, int M, int N, int K, in
     if (cost_single < 0 || w1 * (cand + 32) < cost_single) { cost_single = w1 * (cand + 32); bn_single = cand; }
     if (pairs > 0) {
       const long long w2 = (((M + 255) / 256) * n_tiles + pairs - 1) / pairs;
-      if (cost_pair < 0 || w2 * (cand + 32) < cost_pair) { cost_pair = w2 * (cand + 32); bn_pair = cand; }
+      if (cost_pair < 0 || w2 * (cand + 32) < cost_pair) { cost_pair = w2 * (cand + 32); bn_pair = cand; waves_pair = w2; }
     }
   }
   cudaError_t e;
-  if (pairs > 0 && (cost_pair <= cost_single || g_pair_enabled == 2)) {
+  // At equal cost the pair kernel wins only where a CTA has enough to do: starting and ending a cluster costs it about
+  // 2 us more than the one-CTA kernel (2,048 rows: q/k/v 32.5 against 29.8 us, output projection 20.5 against 18.7, but
+  // down projection, four times as many k-values, 53.3 against 54.8).
+  const long long k_blocks = (K + BK - 1) / BK;
+  const bool pair_wins = cost_pair < cost_single || (cost_pair == cost_single && waves_pair * k_blocks >= 96);
+  if (pairs > 0 && (pair_wins || g_pair_enabled == 2)) {
     const long long m_tiles = (M + 255) / 256;
     const int bn = bn_pair;
     rc = make_map(&map_w, w, (uint64_t)(gate_up ? 2 * N : N), (uint64_t)K, bn / 2);
@@ -682,6 +689,8 @@ int run_product(const void* a, const void* w, void* out, int M, int N, int K, in
 // 0 keeps every product on the one-CTA kernel, 1 (the default) lets products of more than 128 rows go to CTA pairs
 // where the tile plan says they are no slower, 2 sends all of those to CTA pairs (tests).
 SB_EXPORT void sb_gemm_tcgen05_use_pairs(int on) { g_pair_enabled = on; }
+// 0: the tile plan chooses; a multiple of 32 up to 256: every product without gate/up uses tiles of that many columns
+SB_EXPORT void sb_gemm_tcgen05_force_width(int bn) { g_forced_width = bn; }
 SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(gate_up ? EPI_GATE_UP : EPI_STORE, 148); }
 
 // 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).

@@ -483,6 +483,32 @@ def test_tcgen05_product(K, m, n, k, cta_mode):
         assert torch.equal(part, out[m - 64:])
 
 
+@pytest.mark.parametrize("width", [96, 128, 160, 224, 256])
+def test_tcgen05_product_at_every_tile_width(K, width, cta_mode):
+    """The tile plan picks the accumulator width per product (a multiple of 32 columns); every width gives the same
+    numbers, since the order of the k-values in a sum does not depend on it."""
+    m, n, k = 390, 712, 200
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    outs = []
+    K.TCGEN05_MIN_TILES = 1
+    try:
+        for bn in (0, width):
+            K._core.sb_gemm_tcgen05_force_width(bn)
+            out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+            before = K.launches
+            K.linear(a, w, out)
+            assert K.launches == before + 1
+            outs.append(out)
+    finally:
+        K._core.sb_gemm_tcgen05_force_width(0)
+        K.TCGEN05_MIN_TILES = type(K).TCGEN05_MIN_TILES
+    K.check_errors()
+    ref = a.double() @ w.double().T
+    torch.testing.assert_close(outs[1].double(), ref, atol=float(ref.abs().max()) * 2.0 ** -7, rtol=0)
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (2048, 8192, 2048), (300, 384, 200), (130, 128, 72), (64, 256, 96)])
 def test_tcgen05_gate_up_with_swiglu(K, m, inter, k, cta_mode):
     h = torch.randn(m, k, device=DEV).to(torch.bfloat16)
