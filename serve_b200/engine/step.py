@@ -297,13 +297,16 @@ class Stepper:
             while len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             shape = BatchShape(r, r, 1, 1, bucket, True)
-            static_ctx = StepContext(**{**ctx.__dict__, "shape": shape})
+            static_ctx = StepContext(**{**ctx.__dict__, "shape": shape, "memo": {}})
             # warm up outside capture (allocator pools, cuBLAS workspaces, lazy module loads)
             s = torch.cuda.Stream(device=self.rt.device)
             s.wait_stream(torch.cuda.current_stream(self.rt.device))
             with torch.cuda.stream(s), self._pinned_stream():
                 self.model.forward(static_ctx, self.views)
             torch.cuda.current_stream(self.rt.device).wait_stream(s)
+            # what the warm-up derived from the step's arrays must be derived again inside the graph: a replay has
+            # other positions in the same arrays
+            static_ctx.memo.clear()
             graph = torch.cuda.CUDAGraph()
             k = self.rt.kernels
             before = (getattr(k, "launches", 0), getattr(k, "library_calls", 0))

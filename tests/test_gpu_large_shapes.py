@@ -73,3 +73,39 @@ def test_benchmark_widths_match_plain(big, dtype):
         # the whole-prompt step keeps its products on this engine's kernels (only the mixed steps' 65..131-row
         # products go to the library)
         assert eng.kernels.library_calls - library_before < 40
+
+
+SMALL = dict(CFG, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=512)
+
+
+def test_many_rows_decoding_from_graphs_through_the_tensor_memory_products(tmp_path):
+    """Forty requests decode together from CUDA graphs, with every product of more than 32 rows sent to the tcgen05
+    kernels (as happens by itself from about nine hundred rows on): the q/k/v product then takes its cosines and sines
+    from a table made once per step, and a replayed graph must make that table again for its own positions."""
+    from serve_b200.config import EngineConfig, config_from_dict
+    from serve_b200.engine import Engine
+    from serve_b200.weights import write_random_model
+
+    folder = str(tmp_path)
+    write_random_model(folder, config_from_dict(SMALL), seed=3, std=0.05, norm_std=0.1, dtype=torch.bfloat16)
+    cfg, w = helpers.read_folder(folder)
+    n_req, decoded = 40, 5
+    reqs = {f"r{i}": helpers.random_tokens(cfg["vocab_size"], 3 + (i * 7) % 23 + decoded, seed=100 + i) for i in range(n_req)}
+    with torch.no_grad():
+        plain = {rid: llama_forward(w, cfg, toks) for rid, toks in reqs.items()}
+    eng = Engine.from_folder(folder, EngineConfig(dtype="bfloat16", page_size=16, num_pages=n_req * 3, max_slots=n_req,
+                                                  max_tokens_per_step=1024, max_context=64, use_cuda_graphs=True))
+    eng.kernels.TCGEN05_MIN_TILES = 1
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": toks[:-decoded], "want": [len(toks) - decoded - 1]} for rid, toks in reqs.items()],
+              "end": []}]
+    for d in range(decoded):
+        steps.append({"step": d + 1, "entries": [{"id": rid, "tokens": [toks[len(toks) - decoded + d]], "want": [0]}
+                                                  for rid, toks in reqs.items()], "end": []})
+    library_before = eng.kernels.library_calls
+    with torch.inference_mode():
+        got = helpers.replay(eng, steps)
+    eng.kernels.check_errors()
+    assert eng.stepper.launched_graphs >= decoded - 1
+    assert eng.kernels.library_calls - library_before <= len(steps), "only the float logits of each step come from the library"
+    scale = max(float(p.abs().max()) for p in plain.values())
+    helpers.compare_with_plain(got, plain, atol=scale * 2.0 ** -6)
