@@ -2,6 +2,7 @@
 
     python -m serve_b200.kernels.microbench linear --m 8 --n 2048 --k 8192
     python -m serve_b200.kernels.microbench gate_up --m 8 --n 8192 --k 2048
+    python -m serve_b200.kernels.microbench qkv_rope --m 2048 --k 2048 [--unfused]
     python -m serve_b200.kernels.microbench decode_attention --batch 64 --context 2176
     python -m serve_b200.kernels.microbench prefill_attention --tokens 2048
 
@@ -47,7 +48,7 @@ def _time(fn, reps, graph):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m serve_b200.kernels.microbench")
-    ap.add_argument("kernel", choices=["linear", "gate_up", "decode_attention", "prefill_attention"])
+    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=2048)
     ap.add_argument("--k", type=int, default=2048)
@@ -62,6 +63,7 @@ def main(argv=None) -> int:
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--graph", action="store_true")
     ap.add_argument("--legacy-attention", action="store_true", help="prompt attention on the mma.sync kernel instead of tcgen05")
+    ap.add_argument("--unfused", action="store_true", help="qkv_rope: the product, then the rotary kernel")
     ap.add_argument("--library", action="store_true", help="send products to the library (cuBLAS) instead of this engine's kernels")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
@@ -74,7 +76,31 @@ def main(argv=None) -> int:
     if a.legacy_attention:
         K.use_tcgen05_attention = False
     bf = torch.bfloat16
-    if a.kernel in ("linear", "gate_up"):
+    if a.kernel == "qkv_rope":
+        # the q/k/v product of a prompt of --m tokens with rotation and cache write (--heads, --kv-heads, --head-dim)
+        n = (a.heads + 2 * a.kv_heads) * a.head_dim
+        ws = [torch.randn(n, a.k, device=dev, dtype=bf) * 0.02 for _ in range(a.copies)]
+        x = torch.randn(a.m, a.k, device=dev, dtype=bf)
+        qkv = torch.empty(a.m, n, device=dev, dtype=bf)
+        nblk = -(-a.m // a.page_size)
+        kc = torch.zeros(nblk, a.kv_heads, a.page_size, a.head_dim, device=dev, dtype=bf)
+        vc = torch.zeros_like(kc)
+        bt = torch.randperm(nblk, device=dev, dtype=torch.int32).view(1, nblk).contiguous()
+        pos = torch.arange(a.m, device=dev, dtype=torch.int32)
+        row = torch.zeros(a.m, device=dev, dtype=torch.int32)
+        inv = (1.0 / (500000.0 ** (torch.arange(0, a.head_dim, 2).float() / a.head_dim))).to(dev)
+        K.fuse_rope = not a.unfused
+        memo = {}
+
+        def fn():
+            for w in ws:
+                K.qkv_rope_cache(x, w, qkv, pos, row, inv, 1, a.head_dim, a.heads, a.kv_heads, a.head_dim, kc, vc, bt, a.page_size,
+                                 True, memo=memo)
+
+        us = _time(fn, a.reps, a.graph) / a.copies
+        flops = 2.0 * a.m * n * a.k
+        print(f"qkv_rope m={a.m} n={n} k={a.k}{' unfused' if a.unfused else ''}: {us:.2f} us, {flops / us / 1e6:.1f} TFLOP/s")
+    elif a.kernel in ("linear", "gate_up"):
         rows = 2 * a.n if a.kernel == "gate_up" else a.n
         ws = [torch.randn(rows, a.k, device=dev, dtype=bf) * 0.02 for _ in range(a.copies)]
         x = torch.randn(a.m, a.k, device=dev, dtype=bf)
