@@ -84,3 +84,23 @@ def test_schedule_validation():
     for bad in ([ScheduleEntry(5)], [ScheduleEntry(0, cache_of=0)], [ScheduleEntry(0), ScheduleEntry(1, 0), ScheduleEntry(0, 1)], []):
         with pytest.raises(ConfigError):
             dataclasses.replace(spec, schedule=bad).validate()
+
+
+def test_rotary_parts_with_equal_parameters_share_their_frequencies():
+    """What a step derives from the frequencies (the table of cosines and sines) is made once per step only if the
+    layers' position parts hand out the same tensor; other parameters get a tensor of their own."""
+    from serve_b200.config.spec import PartSpec
+    from serve_b200.engine.runtime import Runtime
+    from serve_b200.parts.base import build_part
+
+    rt = Runtime.describe_only()
+    scaling = dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
+    a = build_part("position", PartSpec("rotary", {"rotary_dim": 32, "theta": 10000.0, "scaling": scaling}), rt)
+    b = build_part("position", PartSpec("rotary", {"rotary_dim": 32, "theta": 10000.0, "scaling": dict(scaling)}), rt)
+    c = build_part("position", PartSpec("rotary", {"rotary_dim": 32, "theta": 500000.0, "scaling": scaling}), rt)
+    d = build_part("position", PartSpec("rotary", {"rotary_dim": 32, "theta": 10000.0, "scaling": None}), rt)
+    assert a.inv_freq is b.inv_freq
+    assert c.inv_freq is not a.inv_freq and d.inv_freq is not a.inv_freq
+    assert not bool((c.inv_freq == a.inv_freq).all()) and not bool((d.inv_freq == a.inv_freq).all())
+    other = build_part("position", PartSpec("rotary", {"rotary_dim": 32, "theta": 10000.0, "scaling": scaling}), Runtime.describe_only())
+    assert other.inv_freq is not a.inv_freq and bool((other.inv_freq == a.inv_freq).all())
