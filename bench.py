@@ -23,6 +23,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 PROMPT_LEN = 2048
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+E2E_NEW_TOKENS = 256      # tokens each request generates in the end-to-end runs (both arms)
 
 
 def peaks():
@@ -32,10 +33,11 @@ def peaks():
             with open(path) as f:
                 d = json.load(f)
             return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
-                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    "sm_max_mhz": float(d.get("sm_max_mhz", 1965.0)), "source": "measured"}
         except Exception:
             pass
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "sm_max_mhz": 1965.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -43,19 +45,33 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        self.proc, self.path = None, None
+        self.proc, self.path, self.gpu = None, None, None
+
+    @staticmethod
+    def gpu_in_use():
+        """The UUID of CUDA device 0 of this process ("GPU-..."): nvidia-smi numbers the machine's GPUs its own way,
+        and the visible device need not be its index 0."""
+        try:
+            import torch
+
+            uuid = str(torch.cuda.get_device_properties(0).uuid)
+            return uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            return None
 
     def start(self):
         try:
+            self.gpu = self.gpu_in_use()
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "20"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu or "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "gpu": self.gpu or "index 0"}
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -215,49 +231,73 @@ def prefill_bench(eng, vocab, reps, seed, cuda_profiler=False):
     return times[len(times) // 2]
 
 
-def e2e_bench(eng, batch, steps, vocab, seed, runs=2):
-    """Decoded tokens per second through serve_b200.generate: host token ids in, host token ids out, every step.
-    The timed window is short (about 0.1 s), so one stall of the host (a collection, a page fault) shows as tens of
-    per cent: the load is run ``runs`` times and the fastest window is reported, with the slowest beside it."""
+def e2e_bench(eng, batch, new_tokens, vocab, seed, runs=3):
+    """Generated tokens per second of whole serve_b200.generate() calls: host token ids in, host token ids out, every
+    step, the prompts' prefill included. Timed by the wall clock between device synchronisations, as the reference's own
+    benchmark times its generate() (serve/benchmark.py:63-80); one untimed call first, then the median of ``runs`` calls.
+    ``decode_window`` is the rate inside the pure-decode steps of the median call (from one step's end to the last step's)."""
     import torch
     from serve_b200 import Request, generate
 
     g = torch.Generator().manual_seed(seed)
-    reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, steps + 4) for _ in range(batch)]
-    best = None
-    rates = []
+    reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, new_tokens) for _ in range(batch)]
+    generate(eng, reqs, temperature=0.0)
+    results = []
     for _ in range(runs):
         timeline = []
-        generate(eng, reqs, temperature=0.0, timeline=timeline)
-        dec = [(t, nd, b) for t, npf, nd, b in timeline if nd == batch and npf == 0]
-        # skip the first pure-decode steps (graph capture, warm-up); time from one step's end to the last step's end
-        skip = 3
-        if len(dec) <= skip + 1:
-            return None
-        t0, t1 = dec[skip][0], dec[-1][0]
-        n_steps = len(dec) - 1 - skip
-        rate = batch * n_steps / (t1 - t0)
-        rates.append(rate)
-        if best is None or rate > best["value"]:
-            best = {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": int(dec[-1][2]), "d2h_bytes_per_step": 4 * batch,
-                    "steps": n_steps}
-    best["runs"] = runs
-    best["slowest_run"] = round(min(rates), 1)
-    return best
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = generate(eng, reqs, temperature=0.0, timeline=timeline)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        results.append((sum(len(r.generated_tokens) for r in out) / dt, timeline))
+    results.sort(key=lambda x: x[0])
+    rate, timeline = results[len(results) // 2]
+    dec = [(t, nd, b) for t, npf, nd, b in timeline if nd == batch and npf == 0]
+    rec = {"value": round(rate, 1), "unit": "tokens/s", "what": "whole generate() calls, wall clock, median",
+           "runs": runs, "new_tokens": new_tokens, "slowest_run": round(results[0][0], 1), "fastest_run": round(results[-1][0], 1)}
+    if len(dec) > 4:
+        rec["decode_window"] = round(batch * (len(dec) - 4) / (dec[-1][0] - dec[3][0]), 1)
+        rec["h2d_bytes_per_step"] = int(dec[-1][2])
+        rec["d2h_bytes_per_step"] = 4 * batch
+    return rec
 
 
 def reference_arm(args):
-    """The reference's own benchmark would run here from baseline/_ref. Its offline install fails on this image:
-    `pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref <reference>` stops
-    with "ModuleNotFoundError: No module named 'hatchling'" (the build backend its pyproject.toml names is neither
-    installed nor in the wheelhouse), also from a writable copy and with --no-deps."""
-    installed = os.path.isfile(os.path.join(ROOT, "baseline", "_ref", "serve", "run.py"))
-    why = ("limei1221/serve cannot be installed offline here: its build backend 'hatchling' is neither installed nor in "
-           "/opt/wheelhouse (pip: No module named 'hatchling')")
-    if installed:
-        why = "baseline/_ref holds the reference, but no runner for it was built because the install failed when bench.py was written"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    """limei1221/serve itself at the same configuration (baseline/reference_arm.py); nothing of serve_b200 is imported."""
+    from baseline import reference_arm as arm
+
+    args.warmup = max(args.warmup, 3)
+    return arm.main(args, ClockSampler(), peaks(), {"PROMPT_LEN": PROMPT_LEN, "CONTEXT": CONTEXT, "PREFILL_TOKENS": PREFILL_TOKENS,
+                                                    "E2E_NEW_TOKENS": E2E_NEW_TOKENS})
+
+
+def float32_points(cfg, args, pk):
+    """The same decode step (batch 8) and prefill (2,048 tokens) in true 32-bit: every byte doubles, the products run on
+    the plain FMA units (no tensor-core mode), so the prefill is compared with the FMA peak of the SMs."""
+    import torch
+
+    from serve_b200.config import EngineConfig
+    from serve_b200.engine import Engine
+    from serve_b200.sampling import Sampler
+
+    page, batch = 64, args.batch
+    ec = EngineConfig(dtype="float32", page_size=page, num_pages=(batch + 1) * CONTEXT // page, max_slots=batch + 2,
+                      max_tokens_per_step=max(PROMPT_LEN, PREFILL_TOKENS), max_context=CONTEXT, use_cuda_graphs=not args.no_graphs)
+    eng = Engine.from_config(cfg, seed=0, engine_config=ec)
+    sampler = Sampler(eng.kernels, eng.rt.device, seed=0)
+    weights, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, 4)
+    steps = max(16, args.steps // 4)
+    ms, ctx_mid, _, _ = decode_bench(eng, sampler, batch, steps, args.warmup, cfg.vocab_size, seed=21)
+    achieved = (weights + batch * ctx_mid * kv_per_token) / (ms * 1e-3) / 1e9
+    pre_ms = prefill_bench(eng, cfg.vocab_size, reps=3, seed=27)
+    props = torch.cuda.get_device_properties(0)
+    fma_tflops = props.multi_processor_count * 128 * 2 * pk.get("sm_max_mhz", 1965.0) * 1e6 / 1e12
+    return {"decode_b%d" % batch: round(batch * 1000.0 / ms, 1), "ms_per_step": round(ms, 4), "steps": steps,
+            "roofline_frac": round(achieved / pk["hbm_gbs"], 4), "achieved_gbs": round(achieved, 1),
+            "prefill": {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+                        "frac": round(prefill_flops(PREFILL_TOKENS) / (pre_ms * 1e-3) / (fma_tflops * 1e12), 4),
+                        "peak_tflops": round(fma_tflops, 1), "peak": "SMs x 128 FMA x 2 x max SM clock"}}
 
 
 def main():
@@ -333,7 +373,13 @@ def main():
         pre_ms = prefill_bench(eng, cfg.vocab_size, reps=5, seed=7)
         pre_frac = prefill_flops(PREFILL_TOKENS) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
 
-        e2e = e2e_bench(eng, args.batch, max(args.steps, 32), cfg.vocab_size, seed=9)
+        e2e = e2e_bench(eng, args.batch, E2E_NEW_TOKENS, cfg.vocab_size, seed=9)
+
+        fp32 = None
+        if not args.skip_points:
+            del eng, sampler
+            torch.cuda.empty_cache()
+            fp32 = float32_points(cfg, args, pk)
 
     rec = {
         "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, 2048-token prompts, context 4096)",
@@ -355,6 +401,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "float32": fp32,
         "clocks": clock_rec,
     }
     print(json.dumps(rec))

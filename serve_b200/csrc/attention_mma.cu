@@ -453,10 +453,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
   int hi = p0 + (M - 1) / G + 1;
   {
-    // the request's keys are shared out evenly over the launch's splits, in units of one step of all four warps
+    // the request's keys are shared out evenly over the launch's splits, in units of one step of all the block's
+    // warps. The splits start at the unit boundary at or below the first key, so their size is taken from there:
+    // sized from the first key itself they could end before the last one.
     constexpr int UNIT = NWARPS * DKW;
-    const int split_size = max(UNIT, ((hi - lo + p.num_splits - 1) / p.num_splits + UNIT - 1) / UNIT * UNIT);
     const int base = (lo / UNIT) * UNIT;
+    const int split_size = max(UNIT, ((hi - base + p.num_splits - 1) / p.num_splits + UNIT - 1) / UNIT * UNIT);
     lo = max(lo, base + split * split_size);
     hi = min(hi, base + (split + 1) * split_size);
   }
@@ -468,11 +470,20 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   if (lo >= hi) {
     pdl_launch_dependents();
     pdl_wait();
-    if (tid < 16) {
-      float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
-      ml[0] = -INFINITY; ml[1] = 0.f;
+    if (p.num_splits > 1) {
+      if (tid < 16) {
+        float* ml = p.part_ml + ((((size_t)r * p.Hkv + hk) * p.num_splits + split) * 16 + tid) * 2;
+        ml[0] = -INFINITY; ml[1] = 0.f;
+      }
+      finish_split(p, r, hk, q0, M, NTHR, reinterpret_cast<float*>(smem_raw));
+    } else {
+      // no key at all (a length below the token count): the rows are zeros, as a sum over nothing
+      for (int idx = tid; idx < M * D; idx += NTHR) {
+        const int row = idx / D, d = idx - row * D;
+        const int tok = row / G, hd = hk * G + (row - tok * G);
+        p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(0.f);
+      }
     }
-    if (p.num_splits > 1) finish_split(p, r, hk, q0, M, NTHR, reinterpret_cast<float*>(smem_raw));
     return;
   }
   {

@@ -298,13 +298,13 @@ class Stepper:
                 self._graphs.pop(next(iter(self._graphs)))
             shape = BatchShape(r, r, 1, 1, bucket, True)
             static_ctx = StepContext(**{**ctx.__dict__, "shape": shape, "memo": {}})
-            # warm up outside capture (allocator pools, cuBLAS workspaces, lazy module loads)
-            s = torch.cuda.Stream(device=self.rt.device)
-            s.wait_stream(torch.cuda.current_stream(self.rt.device))
-            with torch.cuda.stream(s), self._pinned_stream():
-                self.model.forward(static_ctx, self.views)
-            torch.cuda.current_stream(self.rt.device).wait_stream(s)
-            # what the warm-up derived from the step's arrays must be derived again inside the graph: a replay has
+            # The first step of a kind runs eagerly, with the grids the graph will have, and its logits are this
+            # step's result (it also warms allocator pools, library workspaces and lazy module loads). The graph is
+            # captured afterwards and first replayed by the next step of the kind: capturing runs nothing, so a
+            # mixer with state of its own sees this step's tokens exactly once.
+            with self._pinned_stream():
+                first = self.model.forward(static_ctx, self.views)
+            # what the eager run derived from the step's arrays must be derived again inside the graph: a replay has
             # other positions in the same arrays
             static_ctx.memo.clear()
             graph = torch.cuda.CUDAGraph()
@@ -315,8 +315,10 @@ class Stepper:
             with torch.cuda.graph(graph, pool=self._graph_pool), self._pinned_stream():
                 out = self.model.forward(static_ctx, self.views)
             counts = (getattr(k, "launches", 0) - before[0], getattr(k, "library_calls", 0) - before[1])
-            g = (graph, out, self._dev, counts)
-            self._graphs[key] = g
+            if hasattr(k, "launches"):
+                k.launches, k.library_calls = before          # capturing launched nothing
+            self._graphs[key] = (graph, out, self._dev, counts)
+            return first
         graph, out, dev, counts = g
         if dev is not self._dev:
             # the packed buffer was re-made larger since capture: capture again

@@ -4,8 +4,10 @@ The reference's LlamaModel, LlamaRMSNorm, LlamaMLP, rotary code and its paged
 cache index (serve/model.py, serve/kv_cache_paged.py) import and run on the
 CPU; only its four Triton entry points cannot, so this script replaces exactly
 those four names with dense torch stand-ins (page writes by loop, softmax
-attention over the gathered pages). Weights are the tiny random models of
-tests/helpers.py, passed through the reference's own conversion rules
+attention over the gathered pages). Weights are the tiny configurations of
+tests/helpers.py with values from a fixed integer stream
+(``helpers.counted_weights``: the same numbers on every machine), passed
+through the reference's own conversion rules
 (serve/hf_utils/convert_hf_checkpoint.py:115-118 permute, :156 fuse, :146-147
 tie). The run is: prefill of the first 5 tokens (its logits are those of
 position 4), then the remaining tokens fed one by one through its decode path.
@@ -16,7 +18,6 @@ tests/test_plain.py compares the plain implementation with the stored outputs.
 import math
 import os
 import sys
-import tempfile
 
 import numpy as np
 import torch
@@ -24,6 +25,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from tests import helpers  # noqa: E402
+
+
+WEIGHT_SEED = 3
 
 
 def install_standins(M):
@@ -73,9 +77,8 @@ def install_standins(M):
 
 
 def run(name, M, KVIndex, page, n_tokens=24, prefill=5):
-    with tempfile.TemporaryDirectory() as tmp:
-        folder = helpers.make_folder(tmp, name, seed=3)
-        cfg, hf = helpers.read_folder(folder)
+    cfg = helpers.TINY[name]
+    hf = helpers.counted_weights(cfg, WEIGHT_SEED, std=helpers.WEIGHT_STD[name], norm_spread=helpers.NORM_STD[name])
     dim, L, H, Hkv, D = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     inter, V = cfg["intermediate_size"], cfg["vocab_size"]
     assert D == dim // H, "the reference derives head_dim from dim // n_heads"
@@ -105,7 +108,7 @@ def run(name, M, KVIndex, page, n_tokens=24, prefill=5):
     m.compute_freqs_cis("cpu")
     kv = [(torch.zeros(256, page, D), torch.zeros(256, page, D)) for _ in range(L)]
     ix = KVIndex(256, page, Hkv, L, 128, 4, "cpu")
-    toks = helpers.random_tokens(V, n_tokens, seed=77)
+    toks = helpers.counted_tokens(V, n_tokens, seed=77)
     rows = []
     with torch.no_grad():
         ix.allocate_requests_batched([0], [prefill])
@@ -118,7 +121,7 @@ def run(name, M, KVIndex, page, n_tokens=24, prefill=5):
             lg = m(torch.tensor([[toks[j]]]), kv, (sl - 1).unsqueeze(1).long(), sl, ix.get_block_table_data([0]), 1, "decode")
             rows.append(lg[0, 0])
     out = os.path.join(HERE, f"reference_{name}.npz")
-    np.savez_compressed(out, tokens=np.array(toks), first_position=prefill - 1, logits=torch.stack(rows).numpy(),
+    np.savez_compressed(out, tokens=np.array(toks), first_position=prefill - 1, logits=torch.stack(rows).numpy(), weight_seed=WEIGHT_SEED,
                         embed_checksum=float(hf["model.embed_tokens.weight"].double().abs().sum()))
     print("wrote", out, torch.stack(rows).shape)
 

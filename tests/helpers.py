@@ -51,6 +51,74 @@ def read_folder(path: str):
     return cfg, w
 
 
+# A shape the reference's own Triton kernels take (pages of 64, head_dim 64): the golden outputs made on a GPU use it.
+GOLDEN_GPU = dict(architectures=["LlamaForCausalLM"], hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=64, intermediate_size=768, vocab_size=512, rms_norm_eps=1e-5,
+                  rope_theta=500000.0,
+                  rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                    original_max_position_embeddings=64),
+                  tie_word_embeddings=False, max_position_embeddings=256)
+
+
+def llama_tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    """Tensor names of a Llama weight file (the left column of serve/hf_utils/convert_hf_checkpoint.py:98-112) and shapes."""
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    nh, nkv, inter, v = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"], cfg["vocab_size"]
+    shapes = {"model.embed_tokens.weight": (v, h), "model.norm.weight": (h,)}
+    if not cfg["tie_word_embeddings"]:
+        shapes["lm_head.weight"] = (v, h)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        shapes.update({p + "self_attn.q_proj.weight": (nh * d, h), p + "self_attn.k_proj.weight": (nkv * d, h),
+                       p + "self_attn.v_proj.weight": (nkv * d, h), p + "self_attn.o_proj.weight": (h, nh * d),
+                       p + "mlp.gate_proj.weight": (inter, h), p + "mlp.up_proj.weight": (inter, h),
+                       p + "mlp.down_proj.weight": (h, inter), p + "input_layernorm.weight": (h,),
+                       p + "post_attention_layernorm.weight": (h,)})
+    return shapes
+
+
+def counted_weights(cfg: dict, seed: int, std: float = 0.05, norm_spread: float = 0.1) -> Dict[str, torch.Tensor]:
+    """Weights that are the same numbers on every machine and under every version of torch and numpy: uniform values
+    from the raw 64-bit stream of numpy's PCG64 (whose stream is fixed by its definition), one stream per tensor name.
+    Matrices are uniform with standard deviation ``std``; norm weights uniform in 1 +- norm_spread."""
+    import hashlib
+
+    import numpy as np
+
+    out = {}
+    for name, shape in llama_tensor_shapes(cfg).items():
+        key = int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little")
+        n = 1
+        for s in shape:
+            n *= s
+        raw = np.random.PCG64(key).random_raw(n)
+        u = (raw >> np.uint64(11)).astype(np.float64) * (1.0 / 9007199254740992.0) * 2.0 - 1.0     # [-1, 1)
+        if len(shape) == 1:
+            vals = 1.0 + norm_spread * u
+        else:
+            vals = u * (std * 3.0 ** 0.5)
+        out[name] = torch.from_numpy(vals.astype(np.float32).reshape(shape))
+    return out
+
+
+def counted_tokens(vocab: int, n: int, seed: int) -> List[int]:
+    """Token ids from the same fixed stream."""
+    import numpy as np
+
+    return (np.random.PCG64(seed).random_raw(n) % np.uint64(vocab)).astype(np.int64).tolist()
+
+
+def write_folder(path: str, cfg: dict, weights: Dict[str, torch.Tensor], dtype=torch.float32) -> str:
+    """A model folder from a config dict and weights by name (through the safetensors package)."""
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(dict(cfg, torch_dtype=str(dtype).replace("torch.", "")), f)
+    save_file({k: v.to(dtype).contiguous() for k, v in weights.items()}, os.path.join(path, "model.safetensors"))
+    return path
+
+
 def random_tokens(vocab: int, n: int, seed: int) -> List[int]:
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()

@@ -189,6 +189,11 @@ ATT_CASES = [
     (3, 1, 256, 16, [5, 1], [37, 50], 0),
     (4, 2, 64, 8, [30, 1, 6], [30, 77, 100], 11),
     (4, 2, 64, 16, [1, 1], [300, 17], 16),
+    # page sizes that are no power of two, or larger than a tile of keys: a tile then crosses pages at odd places
+    (8, 2, 64, 24, [40, 3, 1], [200, 75, 333], 0),
+    (6, 2, 32, 48, [1, 1, 50], [500, 49, 97], 0),
+    (8, 4, 64, 128, [130, 1, 2], [300, 1000, 129], 0),
+    (4, 2, 128, 24, [1, 30], [700, 100], 50),
 ]
 
 
@@ -251,6 +256,32 @@ def test_attention_window_edge(K, dtype):
         assert hit == inside, f"key {back} back: inside={inside}, output max {float(out.float().abs().max()):.3f}"
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("window,length", [(512, 513), (4096, 5000), (4096, 4097), (1000, 1301)])
+def test_decode_attention_with_a_window_over_several_splits_keeps_the_newest_key(K, d, window, length):
+    """Decoding with a window that spans several key splits: only the newest key (the token's own) matches the
+    query, its value is a marker. Splits sized from a first key that lies on no boundary would end before it."""
+    heads, kv_heads, page = 8, 2, 64
+    s = _paged_setup("bfloat16", heads, kv_heads, d, page, q_lens=[1], kv_lens=[length], seed=window)
+    s["qkv"].mul_(0.05); s["kc"].mul_(0.05)
+    for key, marker in ((length - 1, 7.0), (length - window, -3.0), (length - window - 1, 100.0)):
+        pg = int(s["bt"][0, key // page])
+        for kvh in range(kv_heads):
+            s["kc"][pg, kvh, key % page] = 0
+            # the newest key matches strongly, the oldest key inside the window weakly, the first one outside strongly
+            s["kc"][pg, kvh, key % page, :8] = 20.0 if marker != -3.0 else 2.0
+            s["vc"][pg, kvh, key % page] = marker
+    s["qkv"].view(1, heads + 2 * kv_heads, d)[0, :heads, :8] = 20.0
+    out = torch.zeros(1, heads * d, device=DEV, dtype=torch.bfloat16)
+    ref = torch.zeros_like(out)
+    scale = 1.0 / math.sqrt(d)
+    assert K.split_plan(1, kv_heads, length) > 1
+    K.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, window, out, s["shape"])
+    E.attention(s["qkv"], s["kc"], s["vc"], s["bt"], s["cu"], s["kv"], s["row"], s["pos"], heads, kv_heads, d, page, scale, window, ref, s["shape"])
+    torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
+    assert float((out.float() - 7.0).abs().max()) < 0.1
+
+
 def test_refused_sizes(K):
     from serve_b200.kernels import KernelError
 
@@ -305,6 +336,17 @@ MMA_CASES = [
     (8, 4, 16, 4, [3, 129], [1000, 129], 0),
     (8, 2, 64, 8, [60, 1, 2], [200, 400, 90], 37),                            # windows
     (8, 2, 64, 64, [1, 1], [1000, 40], 128),
+    # a window over several key splits whose first key lies on no unit boundary of the splits
+    (8, 2, 64, 64, [1, 1], [5000, 4097], 4096),
+    (8, 2, 128, 64, [1, 1], [5000, 4097], 4096),
+    (32, 8, 64, 64, [1], [513], 512),
+    (8, 2, 64, 32, [2, 1, 1], [2000, 1500, 777], 700),
+    # page sizes that are no power of two, or larger than a tile of keys
+    (32, 8, 64, 24, [1, 1, 1, 70], [2176, 100, 25, 300], 0),
+    (32, 8, 64, 48, [1, 300, 2], [3000, 300, 95], 0),
+    (32, 8, 64, 128, [1, 1, 200, 3], [2176, 129, 1000, 128], 0),
+    (16, 4, 128, 128, [1, 150], [1500, 150], 0),
+    (8, 2, 64, 24, [1, 1], [1000, 40], 100),
 ]
 
 
