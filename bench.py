@@ -160,9 +160,9 @@ def decode_timeline(eng, batch, vocab):
 
     g = torch.Generator().manual_seed(1)
     reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, 24) for _ in range(batch)]
-    generate(eng, reqs, temperature=0.0)
+    generate(eng, reqs, temperature=0.0, eos_token_id=None)
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        generate(eng, reqs, temperature=0.0)
+        generate(eng, reqs, temperature=0.0, eos_token_id=None)
     evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
     firsts = [i for i, e in enumerate(evs) if "embedding" in e.name]
     step = evs[firsts[-5]:firsts[-4]]
@@ -241,13 +241,13 @@ def e2e_bench(eng, batch, new_tokens, vocab, seed, runs=3):
 
     g = torch.Generator().manual_seed(seed)
     reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, new_tokens) for _ in range(batch)]
-    generate(eng, reqs, temperature=0.0)
+    generate(eng, reqs, temperature=0.0, eos_token_id=None)
     results = []
     for _ in range(runs):
         timeline = []
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        out = generate(eng, reqs, temperature=0.0, timeline=timeline)
+        out = generate(eng, reqs, temperature=0.0, eos_token_id=None, timeline=timeline)
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         results.append((sum(len(r.generated_tokens) for r in out) / dt, timeline))

@@ -70,12 +70,28 @@ class _Request:
 
 
 class CacheManager:
+    @staticmethod
+    def group_keys(needs: Sequence[Optional[CacheNeed]]) -> List[Tuple]:
+        """The groups a list of needs forms, in the order the manager numbers them."""
+        keys: List[Tuple] = []
+        for need in needs:
+            if need is not None and need.has_pages and need.group_key() not in keys:
+                keys.append(need.group_key())
+        return keys
+
     def __init__(self, needs: Sequence[Optional[CacheNeed]], cache_of: Sequence[Optional[int]], page_size: int,
-                 num_pages: int, max_slots: int, max_context: int, device=None, kv_dtype=None):
+                 num_pages, max_slots: int, max_context: int, device=None, kv_dtype=None):
         """needs[i]: CacheNeed of schedule entry i if it owns a cache, else None;
         cache_of[i]: the entry whose cache entry i reads, or None.
-        ``num_pages`` is the size of every group's pool. With ``device`` None no
-        device memory is made (host-side tests)."""
+        ``num_pages``: the size of every group's pool, or one size per group (in the
+        order of ``group_keys``). With ``device`` None no device memory is made
+        (host-side tests)."""
+        n_groups = len(self.group_keys(needs))
+        if isinstance(num_pages, int):
+            num_pages = [num_pages] * n_groups
+        num_pages = [int(n) for n in num_pages]
+        if len(num_pages) != n_groups:
+            raise ValueError(f"{len(num_pages)} pool sizes were given for {n_groups} cache groups")
         self.page_size = page_size
         self.max_slots = max_slots
         self.max_blocks = -(-max_context // page_size)
@@ -92,7 +108,7 @@ class CacheManager:
             if key not in key_to_group:
                 key_to_group[key] = len(self.groups)
                 self.groups.append(_Group(key, need.kv_heads, need.head_dim, need.window,
-                                          PagePool(num_pages, len(self.groups)),
+                                          PagePool(num_pages[len(self.groups)], len(self.groups)),
                                           np.full((max_slots, self.max_blocks), -1, dtype=np.int32)))
             self._entry_group.append(key_to_group[key])
         self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None]   # groups that give pages back early
@@ -110,7 +126,7 @@ class CacheManager:
                 if need is None:
                     continue
                 if need.has_pages:
-                    shape = (num_pages, need.kv_heads, page_size, need.head_dim)
+                    shape = (num_pages[self._entry_group[i]], need.kv_heads, page_size, need.head_dim)
                     self._kv[i] = (torch.zeros(shape, dtype=kv_dtype, device=device),
                                    torch.zeros(shape, dtype=kv_dtype, device=device))
                 if need.state_shape is not None:
@@ -118,9 +134,40 @@ class CacheManager:
 
     # ---- sizes ----------------------------------------------------------
     @staticmethod
-    def bytes_per_page(needs: Sequence[Optional[CacheNeed]], page_size: int, itemsize: int) -> int:
-        """Device bytes one page id costs across all executions (K and V)."""
-        return sum(2 * page_size * n.kv_heads * n.head_dim * itemsize for n in needs if n is not None and n.has_pages)
+    def bytes_per_page(needs: Sequence[Optional[CacheNeed]], page_size: int, itemsize: int) -> List[int]:
+        """Per group: device bytes one page id costs across the group's executions (K and V)."""
+        keys = CacheManager.group_keys(needs)
+        out = [0] * len(keys)
+        for n in needs:
+            if n is not None and n.has_pages:
+                out[keys.index(n.group_key())] += 2 * page_size * n.kv_heads * n.head_dim * itemsize
+        return out
+
+    @staticmethod
+    def most_pages_of_a_request(window: Optional[int], page_size: int, length: int, portion: int) -> int:
+        """The most pages one request holds at a time in a group: all of its ``length`` tokens, or, behind a window,
+        what a step of at most ``portion`` new tokens can still read (pages the window has passed were given back)."""
+        full = -(-length // page_size)
+        if window is None:
+            return full
+        return min(full, (window + max(portion, 1) - 2) // page_size + 2)
+
+    def pool_pages(self) -> List[int]:
+        return [g.pool.num_pages for g in self.groups]
+
+    def free_pages(self) -> List[int]:
+        return [g.pool.available for g in self.groups]
+
+    def peak_pages(self, length: int, portion: int) -> List[int]:
+        """Per group: the most pages a request that grows to ``length`` tokens, at most ``portion`` a step, holds at once."""
+        return [self.most_pages_of_a_request(g.window, self.page_size, length, portion) for g in self.groups]
+
+    def pages_held(self, rid: Hashable) -> List[int]:
+        """Per group: pages the request holds now (what closing it gives back)."""
+        r = self._requests.get(rid)
+        if r is None:
+            return [0] * len(self.groups)
+        return [r.reserved[gi] - r.released[gi] for gi in range(len(self.groups))]
 
     def blocks_for(self, length: int) -> int:
         return -(-length // self.page_size)
@@ -179,19 +226,42 @@ class CacheManager:
         return first_key // self.page_size
 
     def pages_wanted(self, rid: Hashable, new_len: int) -> List[int]:
-        """Per group: pages that ``reserve`` would take for this request to reach new_len."""
-        r = self._requests[rid]
-        return [max(0, self.blocks_for(new_len) - r.reserved[gi]) for gi in range(len(self.groups))]
+        """Per group: pages that ``reserve`` would take for this request to reach new_len (a request that is not
+        open counts as a new one)."""
+        r = self._requests.get(rid)
+        nb = self.blocks_for(new_len)
+        if r is None:
+            return [nb] * len(self.groups)
+        return [max(0, nb - r.reserved[gi]) for gi in range(len(self.groups))]
 
-    def can_reserve(self, batch: Sequence[Tuple[Hashable, int]], extra_pages: int = 0) -> bool:
-        want = [extra_pages] * len(self.groups)
+    def fits(self, batch: Sequence[Tuple[Hashable, int]], freed: Sequence[Hashable] = (), at_most: Optional[int] = None) -> bool:
+        """Would ``reserve(batch)`` succeed once the requests in ``freed`` were closed? Changes nothing.
+        ``at_most``: an upper bound the caller knows for the pages any group can want (a request that grows by n
+        tokens wants at most ceil(n / page_size)); if even that many are free, nothing is counted."""
+        n_groups = len(self.groups)
+        if at_most is not None and all(at_most <= g.pool.available for g in self.groups):
+            return True
+        free = [g.pool.available for g in self.groups]
+        gone = set()
+        for rid in freed:
+            r = self._requests.get(rid)
+            if r is not None and rid not in gone:
+                gone.add(rid)
+                for gi in range(n_groups):
+                    free[gi] += r.reserved[gi] - r.released[gi]
+        ps, requests = self.page_size, self._requests
         for rid, new_len in batch:
-            if rid in self._requests:
-                w = self.pages_wanted(rid, new_len)
+            nb = -(-new_len // ps)
+            r = requests.get(rid)
+            if r is None or rid in gone:
+                for gi in range(n_groups):
+                    free[gi] -= nb
             else:
-                w = [self.blocks_for(new_len)] * len(self.groups)
-            want = [a + b for a, b in zip(want, w)]
-        return all(w <= g.pool.available for w, g in zip(want, self.groups))
+                for gi in range(n_groups):
+                    d = nb - r.reserved[gi]
+                    if d > 0:
+                        free[gi] -= d
+        return all(f >= 0 for f in free)
 
     def reserve(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
         """Give every listed request pages up to its new length, or raise OutOfPages and change nothing."""

@@ -8,7 +8,7 @@ the pool (run.py:277). Here they are fields with those values as defaults.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence, Union
 
 from .base import ConfigError
 
@@ -17,7 +17,7 @@ from .base import ConfigError
 class EngineConfig:
     dtype: str = "bfloat16"              # "bfloat16" | "float32"
     page_size: int = 64                  # tokens in a cache page
-    num_pages: Optional[int] = None      # pages per cache group; None: from memory_fraction
+    num_pages: Optional[Union[int, Sequence[int]]] = None   # pages of every cache group, or one count per group; None: from memory_fraction
     memory_fraction: float = 0.6         # share of free device memory for the pools when num_pages is None
     max_slots: int = 256                 # live requests at most
     max_tokens_per_step: int = 2048      # token budget of a step
@@ -33,8 +33,10 @@ class EngineConfig:
             raise ConfigError(f"dtype {self.dtype!r} is not supported (bfloat16, float32)")
         if self.page_size <= 0:
             raise ConfigError("page_size must be positive")
-        if self.num_pages is not None and self.num_pages <= 0:
-            raise ConfigError("num_pages must be positive")
+        if self.num_pages is not None:
+            counts = [self.num_pages] if isinstance(self.num_pages, int) else list(self.num_pages)
+            if not counts or any(int(n) <= 0 for n in counts):
+                raise ConfigError("num_pages must be positive")
         if not (0.0 < self.memory_fraction <= 1.0):
             raise ConfigError("memory_fraction must be in (0, 1]")
         if self.max_slots <= 0 or self.max_tokens_per_step <= 0:

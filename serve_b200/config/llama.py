@@ -9,7 +9,7 @@ heads, head_dim = hidden // heads (model.py:91), untied head, no rope scaling.
 from __future__ import annotations
 
 from dataclasses import dataclass, asdict
-from typing import Any, Dict, Optional
+from typing import Any, Dict, Optional, Tuple
 
 from .base import ConfigError, ModelConfig
 
@@ -76,7 +76,7 @@ class LlamaConfig(ModelConfig):
     max_position_embeddings: int
     torch_dtype: str = "bfloat16"
     bos_token_id: Optional[int] = None
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[Tuple[int, ...]] = None     # every id that ends a sequence (the file may give one or a list)
 
     architecture = "LlamaForCausalLM"
 
@@ -108,7 +108,9 @@ class LlamaConfig(ModelConfig):
             raise ConfigError("rope_scaling must be an object or null")
         eos = d.get("eos_token_id")
         if isinstance(eos, (list, tuple)):
-            eos = int(eos[0]) if eos else None
+            eos = tuple(int(e) for e in eos) or None
+        elif eos is not None:
+            eos = (int(eos),)
         cfg = cls(
             hidden_size=hidden,
             num_hidden_layers=_need(d, "num_hidden_layers"),
@@ -157,5 +159,5 @@ class LlamaConfig(ModelConfig):
         if self.bos_token_id is not None:
             d["bos_token_id"] = self.bos_token_id
         if self.eos_token_id is not None:
-            d["eos_token_id"] = self.eos_token_id
+            d["eos_token_id"] = self.eos_token_id[0] if len(self.eos_token_id) == 1 else list(self.eos_token_id)
         return d

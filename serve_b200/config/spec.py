@@ -30,13 +30,20 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement around a mixer and a feed-forward."""
+    """One layer: a block arrangement (a part with parameters of its own) and the parts it arranges, by the
+    names the arrangement gives them. Which names an arrangement wants, and of which family each is, the
+    arrangement's class says (``Block.wants``): "pre_norm" wants mixer, feed_forward, mixer_norm and
+    feed_forward_norm; an arrangement with other norms, without a feed-forward or with two mixers side by side
+    names other parts, and nothing else changes."""
 
-    block: str                      # registry key of the arrangement, e.g. "pre_norm"
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    block: PartSpec
+    parts: Dict[str, PartSpec]
+
+    @classmethod
+    def pre_norm(cls, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, feed_forward_norm: PartSpec) -> "LayerSpec":
+        """The reference's arrangement (serve/model.py:146-149)."""
+        return cls(PartSpec("pre_norm"), {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": mixer_norm,
+                                          "feed_forward_norm": feed_forward_norm})
 
 
 @dataclass(frozen=True)

@@ -30,9 +30,10 @@ _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 def _head_dims_of(spec) -> Sequence[int]:
     dims = set()
     for layer in spec.layers:
-        hd = layer.mixer.params.get("head_dim")
-        if hd:
-            dims.add(int(hd))
+        for part in layer.parts.values():
+            hd = part.params.get("head_dim")
+            if hd:
+                dims.add(int(hd))
     return sorted(dims)
 
 
@@ -86,14 +87,18 @@ class Engine:
         cache_of = [e.cache_of for e in self.model.schedule]
         num_pages = ec.num_pages
         if num_pages is None:
+            # Every group is sized to the same share of the most it could ever use (every slot at full context, or,
+            # behind a window, what a slot can hold at a time), so that no group runs out long before the others;
+            # the share is what the memory fraction pays for, at most all of it.
+            keys = CacheManager.group_keys(needs)
             per_page = CacheManager.bytes_per_page(needs, ec.page_size, self.dtype.itemsize)
-            if self.rt.device.type == "cuda" and per_page > 0:
+            most = [ec.max_slots * CacheManager.most_pages_of_a_request(key[2], ec.page_size, self.max_context, ec.max_tokens_per_step)
+                    for key in keys]
+            share = 1.0
+            if self.rt.device.type == "cuda" and keys:
                 free, _total = torch.cuda.mem_get_info(self.rt.device)
-                num_pages = max(1, int(free * ec.memory_fraction) // per_page)
-            else:
-                num_pages = 1024
-            # never more than every slot at full context could use
-            num_pages = min(num_pages, ec.max_slots * (-(-self.max_context // ec.page_size)))
+                share = min(1.0, free * ec.memory_fraction / max(1, sum(m * b for m, b in zip(most, per_page))))
+            num_pages = [max(1, int(m * share)) for m in most]
         self.cache = CacheManager(needs, cache_of, ec.page_size, num_pages, ec.max_slots, self.max_context,
                                   device=self.rt.device, kv_dtype=self.dtype)
         self.num_pages = num_pages

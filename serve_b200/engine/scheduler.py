@@ -83,19 +83,17 @@ class Scheduler:
         self.waiting: Deque[SchedRequest] = deque()
         self.running: List[SchedRequest] = []     # in order of admission
         self.finished: List[SchedRequest] = []
-        self.promised_pages = 0                   # reserve_full: pages promised to running requests
+        self.promised = [0] * len(cache.groups)   # reserve_full: pages of each cache group promised to running requests
         self.stats = SchedulerStats()
         self.evicted: List[SchedRequest] = []     # evicted by the last plan(); the caller gives back their cache
 
     # ---- sizes --------------------------------------------------------------
-    def _pool_pages(self) -> int:
-        return min(g.pool.num_pages for g in self.cache.groups) if self.cache.groups else 1 << 30
-
-    def _free_pages(self) -> int:
-        return min(g.pool.available for g in self.cache.groups) if self.cache.groups else 1 << 30
-
-    def _pages(self, tokens: int) -> int:
-        return self.cache.blocks_for(tokens)
+    # Every count of pages is the cache manager's: it knows its groups, their pools, which of them give pages
+    # back behind a window, and what each request holds. The scheduler never turns tokens into pages itself.
+    def _promise(self, req: SchedRequest) -> List[int]:
+        """Per cache group: the most pages the request can hold at a time (the last generated token is never fed
+        back, so the cache holds at most prompt + max_new - 1 tokens)."""
+        return self.cache.peak_pages(len(req.prompt) + req.max_new_tokens - 1, min(self.prefill_chunk, self.budget))
 
     # ---- requests -----------------------------------------------------------
     def add(self, req: SchedRequest) -> None:
@@ -103,13 +101,13 @@ class Scheduler:
             raise ValueError(f"request {req.rid}: empty prompt")
         if req.max_new_tokens < 1:
             raise ValueError(f"request {req.rid}: max_new_tokens must be at least 1")
-        # the last generated token is never fed back, so the cache holds at most prompt + max_new - 1 tokens
         most = len(req.prompt) + req.max_new_tokens - 1
         if most > self.max_context:
             raise ValueError(f"request {req.rid}: prompt of {len(req.prompt)} + {req.max_new_tokens} new tokens exceeds the "
                              f"context limit of {self.max_context}")
-        if self._pages(most) > self._pool_pages():
-            raise ValueError(f"request {req.rid}: needs {self._pages(most)} cache pages, the pool has {self._pool_pages()}")
+        for gi, (need, pool) in enumerate(zip(self._promise(req), self.cache.pool_pages())):
+            if need > pool:
+                raise ValueError(f"request {req.rid}: needs {need} cache pages of group {gi}, the pool has {pool}")
         self.waiting.append(req)
 
     def has_work(self) -> bool:
@@ -121,36 +119,33 @@ class Scheduler:
         (they are listed in ``self.evicted`` for the caller to close in the cache)."""
         self.evicted = []
         while True:
-            entries, need = self._plan_running()
-            if need <= self._free_pages() + self._pages_of(self.evicted):
+            entries, at_most = self._plan_running()
+            batch = [(e.request.rid, e.request.fed + len(e.tokens)) for e in entries]
+            if self.cache.fits(batch, freed=[v.rid for v in self.evicted], at_most=at_most if not self.evicted else None):
                 break
             # pages ran out: the request admitted last goes back to the head of the queue
             victim = self.running.pop()
             self._evict(victim)
-        free_after = self._free_pages() + self._pages_of(self.evicted) - need
         used = sum(len(e.tokens) for e in entries)
-        entries.extend(self._admit(self.budget - used, free_after))
+        entries.extend(self._admit(self.budget - used, batch))
         self.stats.max_running = max(self.stats.max_running, len(self.running))
         return entries
-
-    def _pages_of(self, reqs: Sequence[SchedRequest]) -> int:
-        return sum(self._pages(self.cache.length(r.rid)) if self.cache.is_open(r.rid) else 0 for r in reqs)
 
     def _evict(self, victim: SchedRequest) -> None:
         victim.fed = 0
         victim.preemptions += 1
         self.stats.preemptions += 1
         if self.reserve_full:
-            self.promised_pages -= self._pages(len(victim.prompt) + victim.max_new_tokens - 1)
+            self.promised = [a - b for a, b in zip(self.promised, self._promise(victim))]
         self.evicted.append(victim)
         self.waiting.appendleft(victim)
 
     def _plan_running(self):
-        """(entries of the running requests, cache pages they need beyond what they hold)."""
+        """(entries of the running requests, an upper bound of the pages they want of any cache group)."""
         entries: List[PlannedEntry] = []
         left = self.budget
         ps = self.cache.page_size
-        need = 0
+        at_most = 0
         portions = []
         # decoding requests first: one token each (this loop runs for every live request in every step)
         for r in self.running:
@@ -161,8 +156,7 @@ class Scheduler:
                     tok = gen[-1] if gen else r.prompt[-1]
                     entries.append(PlannedEntry(r, [FROM_DEVICE if tok is None else tok], True))
                     left -= 1
-                    if r.fed % ps == 0:
-                        need += 1                   # its token opens a new page
+                    at_most += 1                    # growing by n tokens takes at most ceil(n / page_size) pages
             elif n > 1:
                 portions.append((r, n))
         # then portions of prompts already under way
@@ -171,41 +165,37 @@ class Scheduler:
                 take = min(n, self.prefill_chunk, left)
                 entries.append(PlannedEntry(r, r.pending()[:take], take == n))
                 left -= take
-                need += -(-(r.fed + take) // ps) - -(-r.fed // ps)
-        return entries, need
+                at_most += -(-take // ps)
+        return entries, at_most
 
-    def _new_pages(self, entries: Sequence[PlannedEntry]) -> int:
-        need = 0
-        for e in entries:
-            r = e.request
-            have = self._pages(r.fed) if self.cache.is_open(r.rid) else 0
-            need += self._pages(r.fed + len(e.tokens)) - have
-        return need
-
-    def _admit(self, left: int, free_pages: int) -> List[PlannedEntry]:
+    def _admit(self, left: int, batch: List) -> List[PlannedEntry]:
+        """Waiting requests, in arrival order, while the token budget, the slots and the pages last. ``batch``: what the
+        running requests already take in this step, as (request, length after the step) pairs."""
         entries: List[PlannedEntry] = []
         free_slots = self.cache.free_slots + len(self.evicted)
+        freed = [v.rid for v in self.evicted]
+        batch = list(batch)
+        pools = self.cache.pool_pages()
         while self.waiting and left > 0 and free_slots > 0:
             r = self.waiting[0]
             if r in self.evicted:
                 break   # evicted in this very step; it waits for the next
             n = r.sequence_length - r.fed
             take = min(n, self.prefill_chunk, left)
-            pages = self._pages(take)
             if self.reserve_full:
-                promise = self._pages(len(r.prompt) + r.max_new_tokens - 1)
-                if self.promised_pages + promise > self.admission_fraction * self._pool_pages() and self.running:
+                promise = self._promise(r)
+                if self.running and any(have + p > self.admission_fraction * pool
+                                        for have, p, pool in zip(self.promised, promise, pools)):
                     break
-                if pages > free_pages:
-                    break
-                self.promised_pages += promise
-            elif pages > free_pages:
+            if not self.cache.fits(batch + [(r.rid, r.fed + take)], freed=freed):
                 break
+            if self.reserve_full:
+                self.promised = [a + b for a, b in zip(self.promised, promise)]
             self.waiting.popleft()
             self.running.append(r)
             entries.append(PlannedEntry(r, r.pending()[:take], take == n))
+            batch.append((r.rid, r.fed + take))
             left -= take
-            free_pages -= pages
             free_slots -= 1
         return entries
 
@@ -239,7 +229,7 @@ class Scheduler:
             self.running.remove(r)
             self.finished.append(r)
             if self.reserve_full:
-                self.promised_pages -= self._pages(len(r.prompt) + r.max_new_tokens - 1)
+                self.promised = [a - b for a, b in zip(self.promised, self._promise(r))]
         return done
 
     def resolve(self, request: SchedRequest, index: int, token: int) -> bool:
@@ -256,7 +246,7 @@ class Scheduler:
             if request in self.running:
                 self.running.remove(request)
                 if self.reserve_full:
-                    self.promised_pages -= self._pages(len(request.prompt) + request.max_new_tokens - 1)
+                    self.promised = [a - b for a, b in zip(self.promised, self._promise(request))]
             if request in self.waiting:
                 self.waiting.remove(request)
             if newly:

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional
 
-from ..config.spec import ModelSpec, PartSpec
+from ..config.spec import ModelSpec
 from ..parts.base import CacheNeed, TensorDecl, build_part
 
 
@@ -20,7 +20,7 @@ class DecoderModel:
         self.spec = spec
         self.rt = runtime
         self.embedding = build_part("embedding", spec.embedding, runtime)
-        self.blocks = [build_part("block", PartSpec(ls.block), runtime, layer_spec=ls) for ls in spec.layers]
+        self.blocks = [build_part("block", ls.block, runtime, parts=ls.parts) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.head, runtime)
         self.schedule = list(spec.schedule)
@@ -60,7 +60,7 @@ class DecoderModel:
             if e.cache_of is not None:
                 needs.append(None)
             else:
-                needs.append(self.blocks[e.layer].mixer.cache_need())
+                needs.append(self.blocks[e.layer].cache_need())
         return needs
 
     # ---- forward -------------------------------------------------------

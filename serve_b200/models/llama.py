@@ -27,8 +27,7 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
         layers.append(
-            LayerSpec(
-                block="pre_norm",
+            LayerSpec.pre_norm(
                 mixer=PartSpec(
                     "attention",
                     {

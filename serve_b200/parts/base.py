@@ -111,7 +111,39 @@ class PositionEncoding(Part):
 
 
 class Block(Part):
-    """An arrangement of norms, mixer and feed-forward around the residual stream."""
+    """An arrangement of parts around the residual stream.
+
+    ``wants`` maps the names the arrangement gives its parts to their families
+    ("mixer", "feed_forward", "norm", ...); the layer description brings one
+    PartSpec per name, the constructor builds each and keeps it as an attribute of
+    that name. ``spec.params`` holds the arrangement's own constants, if it has
+    any. The part named "mixer", if there is one, is the one whose cache the
+    layer owns; an arrangement whose cached part has another name overrides
+    ``cache_need``.
+    """
+
+    wants: Dict[str, str] = {}
+
+    def __init__(self, spec: PartSpec, runtime, parts: Optional[Dict[str, PartSpec]] = None):
+        super().__init__(spec, runtime)
+        given = dict(parts or {})
+        missing = [n for n in self.wants if n not in given]
+        extra = [n for n in given if n not in self.wants]
+        if missing or extra:
+            raise KeyError(f"block {spec.kind!r} arranges the parts {sorted(self.wants)}; the layer description "
+                           f"lacks {sorted(missing)} and has {sorted(extra)} beyond them")
+        self._built = []
+        for name, family in self.wants.items():
+            part = build_part(family, given[name], runtime)
+            setattr(self, name, part)
+            self._built.append(part)
+
+    def parts(self) -> List[Part]:
+        return list(self._built)
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        mixer = getattr(self, "mixer", None)
+        return mixer.cache_need() if mixer is not None else None
 
     def forward(self, x, pending, ctx, cache):
         """(x, pending) -> (x, pending); ``pending`` is a delta not yet added to x."""

@@ -7,20 +7,12 @@ inside the next norm kernel.
 """
 from __future__ import annotations
 
-from .base import Block, build_part, register_part
+from .base import Block, register_part
 
 
 @register_part("block", "pre_norm")
 class PreNormBlock(Block):
-    def __init__(self, spec, runtime, layer_spec=None):
-        super().__init__(spec, runtime)
-        self.mixer_norm = build_part("norm", layer_spec.mixer_norm, runtime)
-        self.mixer = build_part("mixer", layer_spec.mixer, runtime)
-        self.feed_forward_norm = build_part("norm", layer_spec.feed_forward_norm, runtime)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, runtime)
-
-    def parts(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+    wants = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
     def forward(self, x, pending, ctx, cache):
         h = self.mixer_norm.forward(x, pending, ctx)

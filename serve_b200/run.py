@@ -8,7 +8,9 @@
 signature and meaning (run.py:238-308): it returns the requests in the order
 given, each with ``generated_tokens`` and, if asked, the logits of its final
 step. Stopping is by ``max_new_tokens`` as in the reference (run.py:222), and
-by ``eos_token_id`` if one is passed.
+by the end-of-sequence ids of the model's config.json if it names any (or by
+the ids passed as ``eos_token_id``; ``None`` switches that off, which is the
+reference's behaviour).
 
 Command line:  python -m serve_b200.run --model DIR --prompt-ids 1,2,3 --max-new-tokens 16
 """
@@ -61,8 +63,11 @@ def load_model(model_name, device: str = "cuda", dtype=torch.bfloat16, **engine_
 
 @torch.inference_mode()
 def generate(model: Engine, requests: Sequence[Request], temperature: float = 0.0, return_logits: bool = False,
-             seed: int = 0, eos_token_id: Optional[int] = None, timeline: Optional[list] = None) -> List[Request]:
+             seed: int = 0, eos_token_id="config", timeline: Optional[list] = None) -> List[Request]:
     """Run all requests to the end; token ids come from the host and go back to the host every step.
+
+    ``eos_token_id``: an id or several that end a request when generated; "config" (the default) takes the ids the
+    model's configuration names, None stops by length only.
 
     ``timeline``, if a list, receives one record per step after its tokens have reached the host:
     (time.perf_counter(), prompt tokens in the step, decoded tokens in the step, bytes copied to the device)."""
@@ -72,7 +77,16 @@ def generate(model: Engine, requests: Sequence[Request], temperature: float = 0.
     sched = Scheduler(model.cache, ec.max_tokens_per_step, ec.prefill_chunk, ec.reserve_full, ec.admission_fraction,
                       model.max_context)
     sampler = Sampler(model.kernels, model.rt.device, seed)
-    stop = (int(eos_token_id),) if eos_token_id is not None else ()
+    if isinstance(eos_token_id, str):
+        if eos_token_id != "config":
+            raise ValueError('eos_token_id must be an id, a list of ids, None or "config"')
+        eos_token_id = getattr(model.config, "eos_token_id", None)
+    if eos_token_id is None:
+        stop = ()
+    elif isinstance(eos_token_id, (list, tuple)):
+        stop = tuple(int(e) for e in eos_token_id)
+    else:
+        stop = (int(eos_token_id),)
     for i, r in enumerate(requests):
         ids = r.input_ids.tolist() if isinstance(r.input_ids, torch.Tensor) else list(r.input_ids)
         sched.add(SchedRequest(i, ids[: r.input_length], r.max_new_tokens, temperature, stop))
@@ -212,7 +226,9 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt", action="append", default=[], help="text prompt (needs a tokenizer in the model folder)")
     ap.add_argument("--max-new-tokens", type=int, default=32)
     ap.add_argument("--temperature", type=float, default=0.0)
-    ap.add_argument("--eos-token-id", type=int, default=None)
+    ap.add_argument("--eos-token-id", type=int, action="append", default=None,
+                    help="id that ends a request (repeatable); default: the ids config.json names")
+    ap.add_argument("--ignore-eos", action="store_true", help="stop by length only")
     ap.add_argument("--return-logits", action="store_true")
     args = ap.parse_args(argv)
 
@@ -235,7 +251,7 @@ def main(argv=None) -> int:
         ap.error("no prompt given (--prompt-ids, --prompt-file or --prompt)")
     reqs = [Request(torch.tensor(p, dtype=torch.long), len(p), args.max_new_tokens) for p in prompts]
     out = generate(engine, reqs, temperature=args.temperature, return_logits=args.return_logits, seed=args.seed,
-                   eos_token_id=args.eos_token_id)
+                   eos_token_id=None if args.ignore_eos else (args.eos_token_id or "config"))
     for i, r in enumerate(out):
         rec = {"request": i, "generated_tokens": r.generated_tokens.tolist()}
         if tokenizer is not None:

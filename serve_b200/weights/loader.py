@@ -72,7 +72,7 @@ def load_weights(model, model_dir: str, compute_dtype: torch.dtype, device) -> N
     decls = model.tensor_decls()
     ignorable = set(model.ignorable_tensors())
     missing = sorted(n for n in decls if n not in where)
-    unexpected = sorted(n for n in where if n not in decls and n not in ignorable and not n.endswith("rotary_emb.inv_freq"))
+    unexpected = sorted(n for n in where if n not in decls and n not in ignorable)
     wrong = []
     for n, d in decls.items():
         if n in where:

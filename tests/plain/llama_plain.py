@@ -32,17 +32,20 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None, dtype=torch
 
 
 def rotate(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
-    """serve/model.py:234-244 on unpermuted rows: x [T, heads, D], pairs (j, j + D/2)."""
+    """serve/model.py:234-244 on unpermuted rows: x [T, heads, D], pairs (j, j + D/2). Below 32-bit the rotation
+    itself is done in float32 and cast back, as the reference does (model.py:235,244)."""
     d = x.shape[-1]
-    ang = positions.to(inv_freq.dtype)[:, None] * inv_freq[None, :]      # [T, D/2]
+    wide = torch.float32 if x.dtype in (torch.bfloat16, torch.float16) else x.dtype
+    ang = positions.to(inv_freq.dtype if wide != torch.float32 else torch.float32)[:, None] * inv_freq.to(wide)[None, :]      # [T, D/2]
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
-    x1, x2 = x[..., : d // 2], x[..., d // 2:]
-    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+    x1, x2 = x[..., : d // 2].to(wide), x[..., d // 2:].to(wide)
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """serve/model.py:63-68."""
-    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
+    """serve/model.py:63-68: the mean square and the scaling in float32 (or wider), cast back, then times the weight."""
+    wide = x.float() if x.dtype in (torch.bfloat16, torch.float16) else x
+    return (wide * torch.rsqrt(wide.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
 
 
 def swiglu(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
@@ -62,11 +65,11 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     tk, hkv, _ = k.shape
     g = h // hkv
     if q_positions is None:
-        q_positions = torch.arange(tk - tq, tk)
+        q_positions = torch.arange(tk - tq, tk, device=q.device)
     kk = k.repeat_interleave(g, dim=1)
     vv = v.repeat_interleave(g, dim=1)
     s = torch.einsum("thd,shd->hts", q, kk) * scale
-    key_pos = torch.arange(tk)[None, :]
+    key_pos = torch.arange(tk, device=q.device)[None, :]
     mask = key_pos > q_positions[:, None]
     if window:
         mask = mask | (key_pos <= q_positions[:, None] - window)
@@ -102,16 +105,21 @@ def normalise_config(cfg: dict) -> dict:
     return c
 
 
-def llama_forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, schedule=None, window=None) -> torch.Tensor:
+def llama_forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, schedule=None, window=None, device=None,
+                  rows=None) -> torch.Tensor:
     """serve/model.py:196-231 for one whole sequence from position 0: logits [T, V] at every position.
 
-    ``schedule``: list of (layer, cache_of) pairs; default one run of each layer in order."""
+    ``schedule``: list of (layer, cache_of) pairs; default one run of each layer in order.
+    ``device``: where to compute (the weights must lie there already; on a GPU the caller switches TF32 off).
+    ``rows``: positions whose logits are wanted (default all): the head is applied to these only."""
     cfg = normalise_config(cfg)
-    w = {k: v.to(dtype) for k, v in weights.items()}
-    tokens = torch.as_tensor(tokens, dtype=torch.long)
+    w = weights if all(v.dtype == dtype for v in weights.values()) else {k: v.to(dtype) for k, v in weights.items()}
+    tokens = torch.as_tensor(tokens, dtype=torch.long, device=device)
     t = tokens.shape[0]
-    positions = torch.arange(t)
-    inv_freq = rope_inv_freq(cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"]).to(dtype)
+    positions = torch.arange(t, device=device)
+    # frequencies stay 32-bit below 32-bit too: the reference keeps its table of cosines and sines in float32 (model.py:279-283)
+    inv_freq = rope_inv_freq(cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"]).to(
+        torch.float32 if dtype in (torch.bfloat16, torch.float16) else dtype).to(tokens.device)
     eps = cfg["rms_norm_eps"]
     x = w["model.embed_tokens.weight"][tokens]                                           # model.py:220
     if schedule is None:
@@ -127,6 +135,8 @@ def llama_forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, schedul
         hn = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
         x = x + swiglu(hn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])  # :148
     x = rms_norm(x, w["model.norm.weight"], eps)                                         # model.py:223
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long, device=x.device)]
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
     return x @ head.T                                                                    # model.py:227
 

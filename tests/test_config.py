@@ -57,11 +57,11 @@ def test_registry_and_spec():
     cfg = config_from_dict(TINY["b"])
     spec = build_spec(cfg)
     assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
-    att = spec.layers[1].mixer
+    att = spec.layers[1].parts["mixer"]
     assert att.kind == "attention" and att.prefix == "model.layers.1.self_attn."
     assert att.params["heads"] == 6 and att.params["kv_heads"] == 3 and att.params["head_dim"] == 32
     assert att.params["position"].params["scaling"]["factor"] == 8.0
-    assert spec.layers[0].feed_forward.params["intermediate"] == 320
+    assert spec.layers[0].parts["feed_forward"].params["intermediate"] == 320
     assert spec.head.params["tied_to"] is None
     assert build_spec(config_from_dict(TINY["a"])).head.params["tied_to"] == "model.embed_tokens.weight"
 

@@ -11,7 +11,7 @@ from serve_b200.config import EngineConfig, LayerSpec, ModelSpec, PartSpec, Sche
 from serve_b200.engine import Engine, StepEntry
 from serve_b200.engine.runtime import Runtime
 from serve_b200.engine.step import BatchShape, StepContext
-from serve_b200.parts import CacheNeed, FeedForward, Mixer, PositionEncoding, TensorDecl, build_part, register_part
+from serve_b200.parts import Block, CacheNeed, FeedForward, Mixer, PositionEncoding, TensorDecl, build_part, register_part
 from tests import helpers
 from tests.plain import llama_plain as P
 
@@ -137,6 +137,14 @@ class RunningMeanMixer(Mixer):
         return CacheNeed(state_shape=(self.hidden + 1,))
 
     def forward(self, h, ctx, cache):
+        if ctx.shape.pure_decode:
+            # one token per request: device-side indexing only, so that the step can be captured in a graph
+            slots = ctx.slots.long()
+            st = cache.state[slots]
+            sums = st[:, : self.hidden] + h.float()
+            counts = st[:, self.hidden] + 1
+            cache.state[slots] = torch.cat([sums, counts[:, None]], 1)
+            return ((sums / counts[:, None]) @ self.w.float().T).to(h.dtype)
         out = torch.empty_like(h)
         cu = ctx.cu_q.tolist()
         for r, slot in enumerate(ctx.slots.tolist()):
@@ -186,9 +194,9 @@ def _toy_spec(hidden, vocab):
     att = PartSpec("attention", {"hidden": hidden, "heads": 4, "kv_heads": 2, "head_dim": 16, "scale": None, "window": None,
                                  "position": PartSpec("test_none_but_marker", {})}, prefix="l1.att.")
     layers = [
-        LayerSpec("pre_norm", PartSpec("test_running_mean", {"hidden": hidden}, prefix="l0."),
+        LayerSpec.pre_norm(PartSpec("test_running_mean", {"hidden": hidden}, prefix="l0."),
                   PartSpec("test_top1_experts", {"hidden": hidden, "experts": 3}, prefix="l0.moe."), norm("l0.n1."), norm("l0.n2.")),
-        LayerSpec("pre_norm", att, PartSpec("swiglu", {"hidden": hidden, "intermediate": 96}, prefix="l1.mlp."), norm("l1.n1."), norm("l1.n2.")),
+        LayerSpec.pre_norm(att, PartSpec("swiglu", {"hidden": hidden, "intermediate": 96}, prefix="l1.mlp."), norm("l1.n1."), norm("l1.n2.")),
     ]
     return ModelSpec("ToyForTests", hidden, vocab, PartSpec("table", {"vocab": vocab, "hidden": hidden, "name": "emb.weight"}),
                      layers, [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)], norm("final."),
@@ -248,3 +256,145 @@ def test_toy_parts_are_registered_built_and_stepped():
     with torch.inference_mode():
         got = helpers.replay(eng, helpers.trace_portions(reqs, sizes=(5, 2, 11)))
     helpers.compare_with_plain(got, plain, atol=2e-4)
+
+
+def test_a_mixer_with_state_decodes_from_graphs():
+    """The toy model decodes its last tokens from CUDA graphs. The first step of a kind runs eagerly and is then
+    captured; if capture or a warm-up ran the step's kernels a second time, the running-mean mixer would count that
+    token twice and every later logit would be off."""
+    from serve_b200.weights.loader import load_from_source
+    from serve_b200.weights.random_init import random_tensor
+
+    hidden, vocab = 64, 97
+    ec = EngineConfig(dtype="float32", page_size=8, num_pages=48, max_slots=3, max_tokens_per_step=128, max_context=128, use_cuda_graphs=True)
+    eng = Engine(config=None, engine_config=ec, spec=_toy_spec(hidden, vocab))
+    made = {}
+    def source(decl):
+        made[decl.name] = random_tensor(decl, seed=6, std=0.3, norm_std=0.1)
+        return made[decl.name]
+    load_from_source(eng.model, source, torch.float32, DEV)
+    eng._make_cache()
+    reqs = {"x": helpers.random_tokens(vocab, 41, 4), "y": helpers.random_tokens(vocab, 23, 5)}
+    plain = {rid: _toy_plain(made, torch.tensor(t), hidden) for rid, t in reqs.items()}
+    with torch.inference_mode():
+        got = helpers.replay(eng, helpers.trace_tail_decode(reqs, tail=12))
+    assert eng.stepper.launched_graphs >= 20
+    helpers.compare_with_plain(got, plain, atol=2e-4)
+    # two requests decoding side by side are another kind of step (another graph): first sight again
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": t[:10], "want": [9]} for rid, t in reqs.items()], "end": []}]
+    for j in range(10, 23):
+        steps.append({"step": j, "entries": [{"id": rid, "tokens": [t[j]], "want": [0]} for rid, t in reqs.items()], "end": []})
+    with torch.inference_mode():
+        got = helpers.replay(eng, steps)
+    helpers.compare_with_plain(got, plain, atol=2e-4)
+
+
+@register_part("block", "test_sandwich")
+class SandwichBlock(Block):
+    """Another arrangement: every sub-layer has a norm before it and a norm after it (on its output, before the
+    residual sum), and the output of the second is scaled by a constant of the arrangement's own."""
+
+    wants = {"pre_mixer": "norm", "mixer": "mixer", "post_mixer": "norm", "pre_ff": "norm", "feed_forward": "feed_forward",
+             "post_ff": "norm"}
+
+    def __init__(self, spec, runtime, parts=None):
+        super().__init__(spec, runtime, parts)
+        self.ff_scale = float(spec.params.get("ff_scale", 1.0))
+
+    def forward(self, x, pending, ctx, cache):
+        h = self.pre_mixer.forward(x, pending, ctx)
+        a = self.post_mixer.forward(self.mixer.forward(h, ctx, cache).float(), None, ctx)
+        h = self.pre_ff.forward(x, a, ctx)
+        f = self.post_ff.forward(self.feed_forward.forward(h, ctx).float(), None, ctx)
+        return x, f * self.ff_scale
+
+
+WINDOW = 10
+
+
+def _two_kinds_spec(hidden, vocab):
+    norm = lambda p: PartSpec("rms", {"size": hidden, "eps": 1e-5}, prefix=p)
+    rope = PartSpec("rotary", {"rotary_dim": 16, "theta": 10000.0, "scaling": None, "pairing": "half"})
+    att = lambda p, window: PartSpec("attention", {"hidden": hidden, "heads": 4, "kv_heads": 2, "head_dim": 16, "scale": None,
+                                                   "window": window, "position": rope}, prefix=p)
+    ff = lambda p: PartSpec("swiglu", {"hidden": hidden, "intermediate": 96}, prefix=p)
+    layers = [
+        LayerSpec(PartSpec("test_sandwich", {"ff_scale": 0.5}),
+                  {"pre_mixer": norm("l0.n1."), "mixer": att("l0.att.", WINDOW), "post_mixer": norm("l0.n2."),
+                   "pre_ff": norm("l0.n3."), "feed_forward": ff("l0.mlp."), "post_ff": norm("l0.n4.")}),
+        LayerSpec.pre_norm(att("l1.att.", None), ff("l1.mlp."), norm("l1.n1."), norm("l1.n2.")),
+    ]
+    return ModelSpec("TwoKindsForTests", hidden, vocab, PartSpec("table", {"vocab": vocab, "hidden": hidden, "name": "emb.weight"}),
+                     layers, [ScheduleEntry(0), ScheduleEntry(1)], norm("final."),
+                     PartSpec("linear", {"vocab": vocab, "hidden": hidden, "name": "head.weight", "tied_to": None}), 512)
+
+
+def _two_kinds_plain(w, tokens):
+    cfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=16)
+    inv = P.rope_inv_freq(16, 10000.0, None)
+    t = len(tokens)
+    pos = torch.arange(t)
+    n = lambda v, name: P.rms_norm(v, w[name], 1e-5)
+    x = w["emb.weight"][torch.tensor(tokens)]
+    a, _ = P.attention_layer(n(x, "l0.n1.weight"), w, "l0.att.", cfg, pos, inv, WINDOW)
+    x = x + n(a, "l0.n2.weight")
+    f = P.swiglu(n(x, "l0.n3.weight"), w["l0.mlp.gate_proj.weight"], w["l0.mlp.up_proj.weight"], w["l0.mlp.down_proj.weight"])
+    x = x + 0.5 * n(f, "l0.n4.weight")
+    a, _ = P.attention_layer(n(x, "l1.n1.weight"), w, "l1.att.", cfg, pos, inv, None)
+    x = x + a
+    x = x + P.swiglu(n(x, "l1.n2.weight"), w["l1.mlp.gate_proj.weight"], w["l1.mlp.up_proj.weight"], w["l1.mlp.down_proj.weight"])
+    return n(x, "final.weight") @ w["head.weight"].T
+
+
+def test_another_arrangement_and_a_windowed_layer_beside_a_full_one_generate_with_evictions():
+    """A layer of another arrangement (norms after the sub-layers too, defined above) whose attention has a window,
+    beside an ordinary layer with all keys: two cache groups with pools of their own, the windowed one giving pages
+    back while requests run. Greedy generation through the entry point, with portions of 16 tokens and a pool so small
+    that requests are evicted, equals the plain whole-sequence computation token by token; replay in portions and mixed
+    equals it logit by logit."""
+    from serve_b200 import Request, generate
+    from serve_b200.weights.loader import load_from_source
+    from serve_b200.weights.random_init import random_tensor
+
+    hidden, vocab, page = 64, 97, 4
+    made = {}
+    def source(decl):
+        made[decl.name] = random_tensor(decl, seed=8, std=0.25, norm_std=0.1)
+        return made[decl.name]
+    def engine(num_pages, **kw):
+        ec = EngineConfig(dtype="float32", page_size=page, num_pages=num_pages, max_slots=4, max_context=128, **kw)
+        eng = Engine(config=None, engine_config=ec, spec=_two_kinds_spec(hidden, vocab))
+        load_from_source(eng.model, source, torch.float32, DEV)
+        eng._make_cache()
+        return eng
+    eng = engine([24, 30], max_tokens_per_step=128, use_cuda_graphs=False)
+    assert len(eng.cache.groups) == 2 and {g.window for g in eng.cache.groups} == {WINDOW, None}
+    assert eng.cache.pool_pages() == [24, 30]
+    reqs = {"x": helpers.random_tokens(vocab, 41, 1), "y": helpers.random_tokens(vocab, 23, 2), "z": helpers.random_tokens(vocab, 30, 3)}
+    plain = {rid: _two_kinds_plain(made, t) for rid, t in reqs.items()}
+    with torch.inference_mode():
+        got = helpers.replay(eng, helpers.trace_portions(reqs, sizes=(5, 2, 11, 17)))
+        got2 = helpers.replay(eng, helpers.trace_mixed(reqs, live=3, seed=4, budget=24))
+    eng.kernels.check_errors()
+    helpers.compare_with_plain(got, plain, atol=2e-4)
+    helpers.compare_with_plain(got2, plain, atol=2e-4)
+    windowed = next(g for g in eng.cache.groups if g.window)
+    assert windowed.pool.high_water < sum(-(-len(t) // page) for t in reqs.values()), "pages behind the window went back early"
+    # generation, with so few pages of the full group that the scheduler evicts
+    prompts = [reqs["x"][:25], reqs["y"][:9], reqs["z"][:17], reqs["x"][5:18]]
+    n_new = 10
+    want = []
+    for p in prompts:
+        toks = list(p)
+        for _ in range(n_new):
+            toks.append(int(_two_kinds_plain(made, toks)[-1].argmax()))
+        want.append(toks[len(p):])
+    order = [g.window for g in eng.cache.groups]
+    full_pages = -(-(25 + n_new) // page) + 3
+    eng = engine([full_pages if wdw is None else 12 for wdw in order], max_tokens_per_step=32, prefill_chunk=16)
+    out = generate(eng, [Request(torch.tensor(p), len(p), n_new) for p in prompts], temperature=0.0)
+    eng.kernels.check_errors()
+    assert [r.generated_tokens.tolist() for r in out] == want
+    assert eng.last_stats.preemptions > 0
+    eng.cache.check()
+    assert eng.cache.live == 0 and all(g.pool.in_use == 0 for g in eng.cache.groups)
