@@ -159,15 +159,17 @@ def decode_timeline(eng, batch, vocab):
     from serve_b200 import Request, generate
 
     g = torch.Generator().manual_seed(1)
-    reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, 24) for _ in range(batch)]
+    # prompts enter one a step and every request decodes batch + 24 tokens, so for 24 steps all of them decode together;
+    # batch + 5 steps before the end is one of those
+    reqs = [Request(torch.randint(0, vocab, (PROMPT_LEN,), generator=g), PROMPT_LEN, batch + 24) for _ in range(batch)]
     generate(eng, reqs, temperature=0.0, eos_token_id=None)
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         generate(eng, reqs, temperature=0.0, eos_token_id=None)
     evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
     firsts = [i for i, e in enumerate(evs) if "embedding" in e.name]
-    step = evs[firsts[-5]:firsts[-4]]
+    step = evs[firsts[-(batch + 5)]:firsts[-(batch + 4)]]
     t0, prev_end = step[0].time_range.start, step[0].time_range.start
-    print(f"decoding step, batch {batch}: {evs[firsts[-4]].time_range.start - t0:.1f} us from first kernel to the next step's first kernel")
+    print(f"decoding step, batch {batch}: {evs[firsts[-(batch + 4)]].time_range.start - t0:.1f} us from first kernel to the next step's first kernel")
     print(f"{'start us':>9} {'length us':>9} {'vs end of earlier':>17}  kernel")
     for e in step:
         name = e.name.replace("(anonymous namespace)::", "").replace("void ", "")

@@ -241,7 +241,94 @@ int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cuda
   return launch<2, false, 1, GU, false, OutT>(a, w, out, M, N, K, none, stream);
 }
 
+// The same product in true 32-bit arithmetic (plain fused multiply-adds, no tensor-core mode), for the float32 path's
+// decoding steps: a warp owns NC output columns and MB activation rows, its lanes share K out among themselves in
+// steps of four values, partial sums meet by a shuffle tree of fixed order. The weights are read once from memory at
+// streaming speed; the activation rows come from the L1 cache. A row's result does not depend on the other rows.
+constexpr int F32_NC = 4, F32_MB = 8, F32_WARPS = 8;
+
+__device__ __forceinline__ float4 ld_stream_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+__global__ void __launch_bounds__(F32_WARPS * 32, 2) skinny_linear_f32_kernel(const float* __restrict__ a, const float* __restrict__ w,
+                                                                               float* __restrict__ out, int M, int N, int K) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = (blockIdx.x * F32_WARPS + warp) * F32_NC;
+  const int m0 = blockIdx.y * F32_MB;
+  const float* wp[F32_NC];
+  const float* ap[F32_MB];
+#pragma unroll
+  for (int c = 0; c < F32_NC; ++c) wp[c] = w + (size_t)min(n0 + c, N - 1) * K;      // clamped: computed and dropped
+#pragma unroll
+  for (int i = 0; i < F32_MB; ++i) ap[i] = a + (size_t)min(m0 + i, M - 1) * K;
+  float acc[F32_NC][F32_MB];
+#pragma unroll
+  for (int c = 0; c < F32_NC; ++c)
+#pragma unroll
+    for (int i = 0; i < F32_MB; ++i) acc[c][i] = 0.f;
+  // the weights do not depend on the kernel before this one: their first loads go out before the wait
+  float4 wv[F32_NC];
+  int k = lane * 4;
+  if (k < K && n0 < N) {
+#pragma unroll
+    for (int c = 0; c < F32_NC; ++c) wv[c] = ld_stream_f4(wp[c] + k);
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  if (n0 >= N) return;
+  for (; k < K; k += 128) {
+    float4 wn[F32_NC];
+    const int kn = k + 128;
+    if (kn < K) {
+#pragma unroll
+      for (int c = 0; c < F32_NC; ++c) wn[c] = ld_stream_f4(wp[c] + kn);
+    }
+    float4 av[F32_MB];
+#pragma unroll
+    for (int i = 0; i < F32_MB; ++i) av[i] = __ldg(reinterpret_cast<const float4*>(ap[i] + k));
+#pragma unroll
+    for (int c = 0; c < F32_NC; ++c)
+#pragma unroll
+      for (int i = 0; i < F32_MB; ++i) {
+        acc[c][i] = fmaf(wv[c].x, av[i].x, acc[c][i]);
+        acc[c][i] = fmaf(wv[c].y, av[i].y, acc[c][i]);
+        acc[c][i] = fmaf(wv[c].z, av[i].z, acc[c][i]);
+        acc[c][i] = fmaf(wv[c].w, av[i].w, acc[c][i]);
+      }
+    if (kn < K) {
+#pragma unroll
+      for (int c = 0; c < F32_NC; ++c) wv[c] = wn[c];
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < F32_NC; ++c)
+#pragma unroll
+    for (int i = 0; i < F32_MB; ++i) {
+      const float s = warp_sum(acc[c][i]);
+      if (lane == 0 && n0 + c < N && m0 + i < M) out[(size_t)(m0 + i) * N + n0 + c] = s;
+    }
+}
+
 }  // namespace
+
+// 1 if sb_skinny_linear_f32 takes these sizes, else 0 (the caller then uses the library product).
+SB_EXPORT int sb_skinny_linear_f32_supports(int M, int N, int K) {
+  if (M < 1 || M > 32 || N < 1 || K < 4 || (K % 4)) return 0;
+  return 1;
+}
+
+// a [M,K] float, w [N,K] float, out [M,N] float; M <= 32, K a multiple of 4.
+SB_EXPORT int sb_skinny_linear_f32(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
+  if (!sb_skinny_linear_f32_supports(M, N, K)) return SB_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(w)) return SB_ERR_ALIGN;
+  const dim3 grid((N + F32_WARPS * F32_NC - 1) / (F32_WARPS * F32_NC), (M + F32_MB - 1) / F32_MB);
+  SB_PDL_CHECK(launch_pdl(skinny_linear_f32_kernel, grid, dim3(F32_WARPS * 32), 0, stream, (const float*)a, (const float*)w,
+                          (float*)out, M, N, K));
+  return 0;
+}
 
 // 1 if sb_skinny_linear takes these sizes, else 0 (the caller then uses the library product).
 SB_EXPORT int sb_skinny_linear_supports(int M, int N, int K, int gate_up) {

@@ -7,8 +7,10 @@ from __future__ import annotations
 
 import bisect
 import ctypes
+import os
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 from . import build
@@ -74,12 +76,39 @@ def attention_job(head_dim: int):
             "defines": [f"SB_HEAD_DIM={head_dim}"]}
 
 
+def layer_run_job(head_dim: int):
+    # SERVE_B200_STACK_DEFINES: extra -D settings for experiments with the kernel's constants (space separated)
+    extra = os.environ.get("SERVE_B200_STACK_DEFINES", "").split()
+    return {"name": f"sb_stack_hd{head_dim}", "sources": ["decode_stack.cu"], "defines": [f"SB_HEAD_DIM={head_dim}"] + extra}
+
+
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
+# head sizes for which the kernel that runs whole layers of a decoding step is built
+LAYER_RUN_HEAD_DIMS = (64, 128)
+
+# one layer as decode_stack.h lays it out (SbStackLayer)
+_STACK_LAYER = np.dtype([("wqkv", "u8"), ("wo", "u8"), ("wgu", "u8"), ("wdown", "u8"), ("norm1", "u8"), ("norm2", "u8"),
+                         ("inv_freq", "u8"), ("kc", "u8"), ("vc", "u8"), ("eps1", "f4"), ("eps2", "f4"), ("scale_log2", "f4"),
+                         ("rot", "i4"), ("window", "i4"), ("norm_f32", "i4"), ("group", "i4"), ("num_pages", "i4"),
+                         ("write_cache", "i4"), ("pad", "i4")])
+_STACK_MAX_GROUPS = 4
+_STACK_MAX_ROWS = 16
+
+
+class LayerRunPlan:
+    """A run of layers that one launch of the decode-stack kernel takes: the layers' table on the device and what
+    every step needs to call the kernel."""
+
+    def __init__(self, lib, table, keep, n_layers, hidden, heads, kv_heads, head_dim, inter, groups, page_size, blocks):
+        self.lib, self.table, self.keep, self.n_layers = lib, table, keep, n_layers
+        self.hidden, self.heads, self.kv_heads, self.head_dim, self.inter = hidden, heads, kv_heads, head_dim, inter
+        self.groups, self.page_size, self.blocks = groups, page_size, blocks
+        self.takes: Dict[int, bool] = {}
 
 
 def all_jobs():
     """Every library the engine can ask for (the build check compiles them all)."""
-    return core_jobs() + [attention_job(d) for d in SUPPORTED_HEAD_DIMS]
+    return core_jobs() + [attention_job(d) for d in SUPPORTED_HEAD_DIMS] + [layer_run_job(d) for d in LAYER_RUN_HEAD_DIMS]
 
 
 class CudaKernels:
@@ -114,6 +143,15 @@ class CudaKernels:
         self._tickets = []                   # zeroed int32 buffers of the split-key merge (kept alive for graphs)
         self.launches = 0         # launches of this engine's own kernels
         self.library_calls = 0    # library matrix products
+        # Small decoding steps can run all layers in ONE launch (csrc/decode_stack.cu). Measured on a B200 at the
+        # Llama-3.2-1B shape it is slower than the chain of separate kernels (about 80 us a layer against 42), so it is
+        # off unless asked for (tests, and SERVE_B200_LAYER_RUNS=1 for measurements).
+        self.use_layer_runs = os.environ.get("SERVE_B200_LAYER_RUNS", "0") == "1"
+        self._stack: Dict[int, ctypes.CDLL] = {}
+        self._stack_sync = None              # two counters of the layer-run kernel's grid barrier (zero between launches)
+        self._stack_partials = None
+        self.layer_runs = 0                  # launches of the layer-run kernel
+        self.layer_run_timing = None         # profiles: an int64 tensor [layers * 10] that receives block 0's phase stamps
 
     # ---- stream -----------------------------------------------------------
     def on_current_stream(self):
@@ -169,6 +207,8 @@ class CudaKernels:
             n, timeouts = self._errors[:2].tolist()
             if n or timeouts:
                 self._errors.zero_()
+                if self._stack_sync is not None:
+                    self._stack_sync.zero_()     # a barrier that gave up leaves its counters as they were
                 if timeouts:
                     raise KernelError("a wait on a copy or tensor-core barrier inside a kernel ran out; the step's results are not valid")
                 raise KernelError(f"{n} cache writes met a missing page or a block index beyond the block table")
@@ -210,6 +250,9 @@ class CudaKernels:
             elif (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self._tcgen05_worthwhile(m, n)
                     and self._core.sb_gemm_tcgen05_supports(m, n, k, 0)):
                 route = 2
+            elif (a.dtype == torch.float32 and out.dtype == torch.float32 and self.use_skinny_linear
+                    and self._core.sb_skinny_linear_f32_supports(m, n, k)):
+                route = 3
             self._routes[key] = route
         if route == 1:
             self.launches += 1
@@ -217,6 +260,9 @@ class CudaKernels:
         elif route == 2:
             self.launches += 1
             _check(self._core.sb_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, 0, self._wait_flag(), self._s()), "tcgen05 product")
+        elif route == 3:
+            self.launches += 1
+            _check(self._core.sb_skinny_linear_f32(_p(a), _p(w), _p(out), m, n, k, self._s()), "skinny linear, float32")
         else:
             self.library_calls += 1
             _check(self._gemm.sb_linear(_p(a), _p(w), _p(out), m, n, k, _DT[a.dtype], _DT[out.dtype], self._s()), "linear")
@@ -396,6 +442,131 @@ class CudaKernels:
         if not self._tickets or self._tickets[-1].numel() < n:
             self._tickets.append(torch.zeros(max(n, 4096), dtype=torch.int32, device=self.device))
         return self._tickets[-1]
+
+    # ---- whole layers of a decoding step in one launch ---------------------------------------------------------------
+    def _stack_lib(self, head_dim: int):
+        lib = self._stack.get(head_dim)
+        if lib is None:
+            job = layer_run_job(head_dim)
+            job["verbose"] = self._verbose
+            path = build.build_library(**job)
+            self.paths[job["name"]] = path
+            lib = self._stack[head_dim] = ctypes.CDLL(path)
+            lib.sb_decode_stack_partial_floats.restype = ctypes.c_longlong
+            if lib.sb_decode_stack_layer_bytes() != _STACK_LAYER.itemsize:
+                raise KernelError("the layer table's layout on the host and in the library differ")
+        return lib
+
+    def plan_layer_run(self, descs):
+        """(n, plan): the first n of the described layers can run as one launch in a decoding step (n may be 0).
+        ``descs``: what Block.fused_description gives, one per layer in running order."""
+        first = descs[0]
+        if not self._layer_run_describable(first):
+            return 0, None
+        att, ff = first["mixer"], first["feed_forward"]
+        key = (att["hidden"], att["heads"], att["kv_heads"], att["head_dim"], ff["intermediate"], att["page_size"])
+        n = 0
+        groups = []
+        for d in descs:
+            if not self._layer_run_describable(d):
+                break
+            a, f = d["mixer"], d["feed_forward"]
+            if (a["hidden"], a["heads"], a["kv_heads"], a["head_dim"], f["intermediate"], a["page_size"]) != key:
+                break
+            if a["group"] not in groups:
+                if len(groups) == _STACK_MAX_GROUPS:
+                    break
+                groups.append(a["group"])
+            n += 1
+        if n == 0:
+            return 0, None
+        hidden, heads, kv_heads, head_dim, inter, page_size = key
+        lib = self._stack_lib(head_dim)
+        blocks = lib.sb_decode_stack_blocks()
+        if blocks <= 0 or not lib.sb_decode_stack_supports(1, hidden, heads, kv_heads, inter, blocks):
+            return 0, None
+        table = np.zeros(n, dtype=_STACK_LAYER)
+        keep = []
+        for i, d in enumerate(descs[:n]):
+            a, f, n1, n2 = d["mixer"], d["feed_forward"], d["mixer_norm"], d["feed_forward_norm"]
+            row = table[i]
+            row["wqkv"], row["wo"] = a["w_qkv"].data_ptr(), a["w_o"].data_ptr()
+            row["wgu"], row["wdown"] = f["w_gate_up"].data_ptr(), f["w_down"].data_ptr()
+            row["norm1"], row["norm2"] = n1["weight"].data_ptr(), n2["weight"].data_ptr()
+            row["inv_freq"] = a["inv_freq"].data_ptr()
+            row["kc"], row["vc"] = a["k"].data_ptr(), a["v"].data_ptr()
+            row["eps1"], row["eps2"] = n1["eps"], n2["eps"]
+            row["scale_log2"] = a["scale"] * 1.4426950408889634
+            row["rot"], row["window"] = a["rotary_dim"], a["window"]
+            row["norm_f32"] = (1 if n1["weight"].dtype == torch.float32 else 0) | (2 if n2["weight"].dtype == torch.float32 else 0)
+            row["group"] = groups.index(a["group"])
+            row["num_pages"] = a["k"].shape[0]
+            row["write_cache"] = 1 if a["writes"] else 0
+            keep.extend([a["w_qkv"], a["w_o"], f["w_gate_up"], f["w_down"], n1["weight"], n2["weight"], a["inv_freq"], a["k"], a["v"]])
+        dev_table = torch.from_numpy(table.view(np.uint8).copy()).to(self.device)
+        return n, LayerRunPlan(lib, dev_table, keep, n, hidden, heads, kv_heads, head_dim, inter, groups, page_size, blocks)
+
+    @staticmethod
+    def _layer_run_describable(d) -> bool:
+        if d is None or d.get("kind") != "pre_norm":
+            return False
+        a, f, n1, n2 = d.get("mixer"), d.get("feed_forward"), d.get("mixer_norm"), d.get("feed_forward_norm")
+        if not (a and f and n1 and n2) or a.get("kind") != "attention" or f.get("kind") != "swiglu":
+            return False
+        if n1.get("kind") != "rms" or n2.get("kind") != "rms":
+            return False
+        if a["head_dim"] not in LAYER_RUN_HEAD_DIMS or a["w_qkv"].dtype != torch.bfloat16 or a["k"] is None or a["k"].dtype != torch.bfloat16:
+            return False
+        if a["rotary_dim"] > 0 and a["pairing"] != 1:
+            return False
+        if a["rotary_dim"] % 2 or n1["size"] != a["hidden"] or n2["size"] != a["hidden"] or f["hidden"] != a["hidden"]:
+            return False
+        return all(n["weight"].dtype in (torch.float32, torch.bfloat16) for n in (n1, n2))
+
+    def layer_run_takes(self, plan: LayerRunPlan, ctx) -> bool:
+        """Does this step go through the one-launch kernel? Decoding steps (one token per request) of at most 16 requests."""
+        shape = ctx.shape
+        if not (self.use_layer_runs and shape.pure_decode and shape.tokens <= _STACK_MAX_ROWS):
+            return False
+        ok = plan.takes.get(shape.tokens)
+        if ok is None:
+            ok = plan.takes[shape.tokens] = bool(plan.lib.sb_decode_stack_supports(shape.tokens, plan.hidden, plan.heads, plan.kv_heads,
+                                                                                  plan.inter, plan.blocks))
+        return ok
+
+    def layer_run(self, plan: LayerRunPlan, x, pending, ctx):
+        """Runs the plan's layers on the step's tokens: x [M, hidden] float32 is updated in place; returns (x, pending)."""
+        m = x.shape[0]
+        dev = x.device
+        act = lambda cols: torch.empty((m, cols), dtype=torch.bfloat16, device=dev)
+        n_qkv = (plan.heads + 2 * plan.kv_heads) * plan.head_dim
+        x_scratch = torch.empty_like(x)
+        delta_o, delta_down = act(plan.hidden), act(plan.hidden)
+        qkv, attn, inter = act(n_qkv), act(plan.heads * plan.head_dim), act(plan.inter)
+        num_splits = max(1, min(plan.blocks // max(1, m * plan.kv_heads), -(-ctx.shape.max_kv // 256), self.MAX_SPLITS))
+        partials = tickets = None
+        if num_splits > 1:
+            need = plan.lib.sb_decode_stack_partial_floats(_STACK_MAX_ROWS, plan.kv_heads, self.MAX_SPLITS)
+            if self._stack_partials is None or self._stack_partials.numel() < need:
+                self._stack_partials = torch.empty(need, dtype=torch.float32, device=self.device)
+                self._keep.append(self._stack_partials)
+            partials = self._stack_partials
+            tickets = self._ticket_buffer(m * plan.kv_heads)
+        if self._stack_sync is None:
+            self._stack_sync = torch.zeros(4, dtype=torch.int32, device=self.device)
+        tables = (ctypes.c_void_p * _STACK_MAX_GROUPS)()
+        widths = (ctypes.c_int * _STACK_MAX_GROUPS)()
+        for i, g in enumerate(plan.groups):
+            tables[i] = ctx.block_tables[g].data_ptr()
+            widths[i] = ctx.block_tables[g].shape[1]
+        self.launches += 1
+        self.layer_runs += 1
+        _check(plan.lib.sb_decode_stack(
+            _p(plan.table), plan.n_layers, m, plan.hidden, plan.heads, plan.kv_heads, plan.inter, _p(ctx.positions), _p(ctx.kv_len),
+            tables, widths, len(plan.groups), plan.page_size, _p(x), _p(x_scratch), _p(pending), _p(delta_o), _p(delta_down),
+            _p(qkv), _p(attn), _p(inter), _p(partials), _p(tickets), num_splits, _p(self._stack_sync), _p(self.errors_tensor()),
+            plan.blocks, _p(self.layer_run_timing), self._s()), "layers of a decoding step")
+        return x, delta_down
 
     def sample(self, logits, temperature, req_ids, tok_index, seed, out, slots=None, last_token=None) -> None:
         self.launches += 1

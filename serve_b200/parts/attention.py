@@ -83,6 +83,13 @@ class Attention(Mixer):
     def cache_need(self):
         return CacheNeed(kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window)
 
+    def fused_description(self, cache):
+        """What a kernel that runs whole layers at once needs to know of this mixer (tensors and constants)."""
+        return dict(kind="attention", hidden=self.hidden, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
+                    w_qkv=self.w_qkv, w_o=self.w_o, rotary_dim=self.position.rotary_dim, pairing=self.pairing,
+                    inv_freq=self.position.inv_freq, scale=self.scale, window=self.window or 0, k=cache.k, v=cache.v,
+                    group=cache.group, writes=cache.writes, page_size=cache.page_size)
+
     def forward(self, h, ctx, cache):
         rt = self.rt
         t = h.shape[0]

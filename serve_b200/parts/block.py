@@ -14,6 +14,17 @@ from .base import Block, register_part
 class PreNormBlock(Block):
     wants = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
+    def fused_description(self, cache):
+        """This arrangement with its parts' own descriptions, for kernels that run whole layers at once; None if a part
+        has no description to give (such a layer runs part by part)."""
+        out = {"kind": "pre_norm"}
+        for name in self.wants:
+            describe = getattr(getattr(self, name), "fused_description", None)
+            if describe is None:
+                return None
+            out[name] = describe(cache) if name == "mixer" else describe()
+        return out
+
     def forward(self, x, pending, ctx, cache):
         h = self.mixer_norm.forward(x, pending, ctx)
         a = self.mixer.forward(h, ctx, cache)

@@ -38,6 +38,10 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([tensors[self.gate_name], tensors[self.up_name]], dim=0).contiguous()
         self.w_down = tensors[self.down_name].contiguous()
 
+    def fused_description(self):
+        """What a kernel that runs whole layers at once needs to know of this feed-forward."""
+        return dict(kind="swiglu", hidden=self.hidden, intermediate=self.intermediate, w_gate_up=self.w_gate_up, w_down=self.w_down)
+
     def forward(self, h, ctx):
         rt = self.rt
         t = h.shape[0]

@@ -28,6 +28,10 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.weight = tensors[self.weight_name]
 
+    def fused_description(self):
+        """What a kernel that runs whole layers at once needs to know of this norm."""
+        return dict(kind="rms", size=self.size, eps=self.eps, weight=self.weight)
+
     def forward(self, x, delta, ctx):
         out = self.rt.empty_act((x.shape[0], self.size))
         self.rt.kernels.add_rmsnorm(x, delta, self.weight, self.eps, out)

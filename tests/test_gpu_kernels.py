@@ -92,6 +92,27 @@ def test_linear_float32_is_not_a_reduced_precision_mode(K):
     assert float((out.double() - ref).abs().max()) < 2e-4
 
 
+@pytest.mark.parametrize("m", [1, 7, 8, 9, 17, 32, 33])
+@pytest.mark.parametrize("n,k", [(2048, 2048), (331, 72), (5, 4), (1000, 8192), (128256, 256)])
+def test_few_rows_product_in_true_float32(K, m, n, k):
+    """Up to 32 rows in float32 run on the engine's own plain-arithmetic kernel (33 go to the library): against
+    float64, with a bound that a reduced-precision matrix mode would miss by orders of magnitude, and row by row
+    the same bits whatever the number of rows."""
+    g = torch.Generator(device="cpu").manual_seed(m * 1000 + k)
+    a = torch.randn(m, k, generator=g).to(DEV)
+    w = torch.randn(n, k, generator=g).to(DEV)
+    out = torch.full((m, n), float("nan"), device=DEV)
+    before = K.launches
+    K.linear(a, w, out)
+    assert (K.launches == before + 1) == (m <= 32)
+    ref = a.double() @ w.double().T
+    assert float((out.double() - ref).abs().max()) <= 3e-7 * math.sqrt(k) * float(ref.abs().max())
+    if 1 < m <= 32:
+        alone = torch.empty(1, n, device=DEV)
+        K.linear(a[m - 1:m].contiguous(), w, alone)
+        assert torch.equal(alone[0], out[m - 1])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("t,inter", [(3, 200), (17, 8192), (1, 1)])
 def test_swiglu(K, dtype, t, inter):
