@@ -221,3 +221,55 @@ def main(args, clock_sampler, peaks, consts):
     }
     print(json.dumps(rec))
     return 0
+
+
+def offline_load(which: str, num_sequences: int = 2000) -> int:
+    """The reference's own benchmark load (serve/benchmark.py:12-24: lengths uniform in 1..256, seeds 1352, temperature
+    0.6) on random weights of its 1B or 8B configuration: one untimed run, then the timed run, as its benchmark does
+    (benchmark.py:63-80). The model is built on the GPU directly (no checkpoint file of 16 GB is written)."""
+    sys.path.insert(0, REF)
+    sys.dont_write_bytecode = True
+    import torch
+
+    import serve.run as run
+    from serve.model import LlamaModel, ModelArgs
+    from serve.utils import config_1b, config_8b
+
+    import random       # (serve/benchmark.py itself is not imported: its module body loads a checkpoint from the hub)
+
+    config = dict(config_1b if which == "1b" else config_8b)
+    with torch.device("cuda"):
+        model = LlamaModel(ModelArgs(**config), dtype=torch.bfloat16).to(torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if name.endswith("norm.weight"):
+                p.fill_(1.0)
+            else:
+                p.copy_((torch.randn(p.shape, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(p.dtype))
+    model.compute_freqs_cis("cuda")
+    model = model.eval()
+    random.seed(1352)
+    torch.manual_seed(1352)
+    reqs = []
+    for _ in range(num_sequences):                       # serve/benchmark.py:12-24
+        n_in, n_out = random.randint(1, 256), random.randint(1, 256)
+        reqs.append(run.Request(input_ids=torch.randint(0, 10000, (n_in,), dtype=torch.long), input_length=n_in, max_new_tokens=n_out))
+    t0 = time.perf_counter()
+    run.generate(model, reqs, 0.6)
+    print(f"Warmup time: {time.perf_counter() - t0:.4f} seconds")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = run.generate(model, reqs, 0.6)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    total = sum(len(r.generated_tokens) for r in out)
+    print(f"Time taken: {dt:.4f} seconds")
+    print(f"Throughput: {total / dt:.2f} tokens/second")
+    return 0
+
+
+if __name__ == "__main__":
+    if len(sys.argv) >= 3 and sys.argv[1] == "--offline":
+        sys.exit(offline_load(sys.argv[2], int(sys.argv[3]) if len(sys.argv) > 3 else 2000))
+    sys.exit("usage: python baseline/reference_arm.py --offline 1b|8b [requests]   (bench.py --impl reference runs the benchmark arm)")

@@ -7,7 +7,7 @@ and state slots, one step function for mixed batches, a scheduler with chunked
 prefill, sampling, and hand-written sm_100a kernels underneath.
 """
 from . import models, parts  # noqa: F401  (register architectures and parts)
-from .config import EngineConfig, LlamaConfig, load_config, load_preset  # noqa: F401
+from .config import EngineConfig, load_config, load_preset  # noqa: F401
 from .engine import Engine, StepEntry  # noqa: F401
 
 from .run import Request, generate, load_model  # noqa: F401,E402

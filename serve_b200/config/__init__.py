@@ -3,6 +3,5 @@ from .base import (  # noqa: F401
     lookup_architecture, register_architecture,
 )
 from .engine import EngineConfig, normalize_dtype  # noqa: F401
-from .llama import LlamaConfig, RopeScaling  # noqa: F401
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry  # noqa: F401
 from .presets import load_preset, preset_names  # noqa: F401

@@ -776,7 +776,7 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
     }
     // bit 2 of ``which``: some request has more than 8 rows (the caller knows the largest token count).
     // Few blocks (at most one per SM): 8 warps each, so that an SM still has warps to switch between.
-    const bool roomy = (long long)n_rows * Hkv * num_splits <= 148 && deep_smem_bytes(8) <= 227 * 1024;
+    const bool roomy = (long long)n_rows * Hkv * num_splits <= sm_count() && deep_smem_bytes(8) <= 227 * 1024;
     // Very many (request, kv head) pairs, as in a large batch of short requests: one warp per pair. Seven such
     // blocks share an SM, so the fixed part of a pair's time (table, queries, first loads, store) overlaps with
     // six other pairs' key loops instead of being paid once per four-warp block.
@@ -855,7 +855,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
     e = cudaMemsetAsync(tickets, 0, (size_t)n_rows * Hkv * sizeof(int), stream);
     if (e != cudaSuccess) return (int)e;
   }
-  const bool roomy = (long long)n_rows * Hkv * num_splits <= 148 && deep_smem_bytes(8) <= 227 * 1024;
+  const bool roomy = (long long)n_rows * Hkv * num_splits <= sm_count() && deep_smem_bytes(8) <= 227 * 1024;
   int rc = roomy ? launch_deep<false, 8>(p, n_rows, stream) : launch_deep<false, 4>(p, n_rows, stream);
   if (rc) return rc;
   if ((long long)max_q * G > 8 || G > 8) {

@@ -305,7 +305,7 @@ struct Cursor {
 // One warp per row; a lane's loads go out together (16 float4 at a time), sums in index order within a lane, then a
 // fixed shuffle tree. Rows of up to 2,048 values stay in registers between the sum and the scaling.
 #ifndef SB_STACK_NV
-#define SB_STACK_NV 16
+#define SB_STACK_NV 4
 #endif
 constexpr int NV = SB_STACK_NV;
 

@@ -171,11 +171,14 @@ static int launch_add_rmsnorm(float* x, const void* delta, const int* rows, cons
     int threads = nvec <= 128 ? 128 : (nvec <= 256 ? 256 : 512);
     const int vpt = (nvec + threads - 1) / threads;
     if (vpt <= 8) {
-    // With many rows the kernel is launched ahead of its predecessor's end (its blocks then wait inside). With few
-    // rows that was measured to hurt: a decoding step's chain of short kernels ran 0.89 ms with this kernel as a full
-    // stop between the products and 1.23 ms without one, because blocks of the products two and three launches ahead
-    // then sit on the SMs, waiting, in place of blocks of the product that is running.
-    const bool ahead = n_rows > 32;
+    // The kernel is launched ahead of its predecessor's end (its blocks then wait inside). With the few rows of a
+    // decoding step that once hurt: this kernel lets its own successor in at once, so blocks of products two and three
+    // launches ahead sat on the SMs, waiting, in place of blocks of the product that was running (1.23 ms a step against
+    // 0.89 ms with this kernel as a full stop). The products that come before a norm therefore let their successor in
+    // only when their own work is done (skinny_linear.cu, late_trigger); with that, launching this kernel ahead gains
+    // 1-1.5 % of a decoding step (0.802 -> 0.791 ms at batch 8). SERVE_B200_EARLY_TRIGGER=1 brings the full stop back.
+    static const bool late = getenv("SERVE_B200_EARLY_TRIGGER") == nullptr;
+    const bool ahead = n_rows > 32 || late;
 #define SB_NORM_VEC(WT, VPT)                                                                                              \
   do {                                                                                                                    \
     if (ahead) {                                                                                                          \
@@ -268,12 +271,12 @@ SB_EXPORT int sb_swiglu(const void* gate_up, void* out, int n_tokens, int inter,
   if (dtype == SB_DTYPE_BF16 && (inter % 8) == 0 && aligned16(gate_up) && aligned16(out)) {
     const size_t total8 = total / 8;
     const size_t want = (total8 + threads - 1) / threads;
-    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const int blocks = (int)(want < sm_count() * 16 ? want : sm_count() * 16);
     swiglu_bf16_vec_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter / 8, total8);
     SB_LAUNCH_CHECK();
     return 0;
   }
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  const int blocks = (int)((total + threads - 1) / threads < sm_count() * 16 ? (total + threads - 1) / threads : sm_count() * 16);
   if (dtype == SB_DTYPE_F32)
     swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
   else if (dtype == SB_DTYPE_BF16)
@@ -418,7 +421,7 @@ SB_EXPORT int sb_rope_cache_write(void* qkv, const int* positions, const int* to
       (!write_cache || (aligned16(kc) && aligned16(vc)))) {
     const long long total = (long long)n_tokens * (H + 2 * Hkv) * (D / 8);
     const long long want = (total + 255) / 256;
-    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const int blocks = (int)(want < sm_count() * 16 ? want : sm_count() * 16);
     SB_PDL_CHECK(launch_pdl(rope_cache_write_vec_kernel, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)qkv, positions, token_row,
                             inv_freq, rot, H, Hkv, D, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table, bt_width, ps, num_pages,
                             write_cache, n_tokens, errors));
@@ -466,7 +469,7 @@ SB_EXPORT int sb_rope_angles(const int* positions, const float* inv_freq, int ro
   if ((rot & 1) || !positions || !inv_freq || !out || ((uintptr_t)out & 7)) return SB_ERR_SHAPE;
   const long long total = (long long)n_tokens * (rot / 2);
   const long long want = (total + 255) / 256;
-  rope_angles_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(positions, inv_freq, rot / 2, n_tokens, (float2*)out);
+  rope_angles_kernel<<<(int)(want < sm_count() * 8 ? want : sm_count() * 8), 256, 0, stream>>>(positions, inv_freq, rot / 2, n_tokens, (float2*)out);
   return (int)cudaGetLastError();
 }
 

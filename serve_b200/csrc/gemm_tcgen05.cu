@@ -624,11 +624,7 @@ int run_product(const void* a, const void* w, void* out, int M, int N, int K, in
   CUtensorMap map_a, map_w;
   int rc = make_map(&map_a, a, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
-  int sms = 148;
-  {
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  const int sms = sm_count();
   // Tile plan. A wave of tiles takes about (tile width + a fixed part worth 32 columns) whether its tiles are 128 rows
   // on one CTA or 256 rows on a CTA pair (each SM works on 128 rows either way), so the two kernels' costs compare
   // directly: whole waves needed x that time, for the best width of each. Ragged row counts decide it: 330 rows are
@@ -691,7 +687,7 @@ int run_product(const void* a, const void* w, void* out, int M, int N, int K, in
 SB_EXPORT void sb_gemm_tcgen05_use_pairs(int on) { g_pair_enabled = on; }
 // 0: the tile plan chooses; a multiple of 32 up to 256: every product without gate/up uses tiles of that many columns
 SB_EXPORT void sb_gemm_tcgen05_force_width(int bn) { g_forced_width = bn; }
-SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(gate_up ? EPI_GATE_UP : EPI_STORE, 148); }
+SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(gate_up ? EPI_GATE_UP : EPI_STORE, sm_count()); }
 
 // 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).
 SB_EXPORT int sb_gemm_tcgen05_supports(int M, int N, int K, int gate_up) { return supports(M, N, K, gate_up ? EPI_GATE_UP : EPI_STORE); }

@@ -50,6 +50,7 @@ struct RopeArgs {
   const int* block_table;
   int bt_width, ps, num_pages, write_cache;
   int* errors;
+  int late_trigger;    // let the kernel after this one start only when this kernel's products are done (see launch_mt)
 };
 
 // MT: tiles of 16 activation rows (M <= 16*MT); HALF: only rows 0..7 of the single tile exist (M <= 8).
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
       for (int u = 0; u < NB; ++u) vw[j][u] = ld_stream(wp[u] + off);
     }
   }
-  pdl_launch_dependents();
+  if (!ra.late_trigger) pdl_launch_dependents();
   pdl_wait();
   for (int gi = g_lo; gi < g_hi; gi += UNROLL) {
     uint4 vg[UNROLL][MT], vh[UNROLL][MT];
@@ -145,6 +146,7 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
       }
     }
   }
+  if (ra.late_trigger) pdl_launch_dependents();
   // partial sums of the 8 warps -> shared memory; element (m_local, n_local) of a tile at m_local*8 + n_local
 #pragma unroll
   for (int u = 0; u < NB; ++u)
@@ -222,13 +224,18 @@ int launch(const void* a, const void* w, void* out, int M, int N, int K, const R
 // them, 16-column blocks do the same work in fewer, fatter blocks (each pays its fixed part once): measured on the 1B
 // shapes, q/k/v (384 -> 192 blocks) and gate/up (1024 -> 512) gained 4 % of a decoding step each.
 inline bool wide_blocks(int N) {
-  int sms = 148;
+  int sms = sm_count();
   return (N + 7) / 8 > 2 * sms;
 }
 
 template <bool GU, typename OutT>
 int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
-  const RopeArgs none = {};
+  RopeArgs none = {};
+  // A plain product with bfloat16 output is followed by the add + norm kernel (a handful of blocks). If that kernel
+  // is launched ahead, it should come in when this kernel's products are done, not when they start: it would release
+  // its own successor at once, and blocks of kernels two and three launches ahead would take the places of running ones.
+  static const bool late = getenv("SERVE_B200_EARLY_TRIGGER") == nullptr;
+  none.late_trigger = (late && !GU && sizeof(OutT) == 2) ? 1 : 0;
   const bool wide = wide_blocks(N);
   if (M <= 8) {
     if (wide) return launch<1, true, 2, GU, false, OutT>(a, w, out, M, N, K, none, stream);
@@ -363,7 +370,7 @@ SB_EXPORT int sb_skinny_qkv_rope(const void* a, const void* w, void* out, int M,
   RopeArgs ra;
   ra.positions = positions; ra.token_row = token_row; ra.inv_freq = inv_freq; ra.rot = rot; ra.H = H; ra.Hkv = Hkv; ra.D = D;
   ra.kc = (bf16*)kc; ra.vc = (bf16*)vc; ra.block_table = block_table; ra.bt_width = bt_width; ra.ps = ps; ra.num_pages = num_pages;
-  ra.write_cache = write_cache; ra.errors = errors;
+  ra.write_cache = write_cache; ra.errors = errors; ra.late_trigger = 0;
   const bool wide = wide_blocks(N);
   if (M <= 8) {
     if (wide) return launch<1, true, 2, false, true, bf16>(a, w, out, M, N, K, ra, stream);

@@ -11,7 +11,6 @@ replaces both.
 """
 from __future__ import annotations
 
-import contextlib
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -109,9 +108,8 @@ class Stepper:
         self.last_slots = None      # device view of the state slots of the last step's rows
 
     def _pinned_stream(self):
-        """The kernels object may look the current stream up once for a whole forward pass."""
-        pin = getattr(self.rt.kernels, "on_current_stream", None)
-        return pin() if pin is not None else contextlib.nullcontext()
+        """The kernels object looks the current stream up once for a whole forward pass."""
+        return self.rt.kernels.on_current_stream()
 
     # ---- buffers ----------------------------------------------------------
     def _buffers(self, n: int):
@@ -239,11 +237,7 @@ class Stepper:
         for gi, (off, rr, w) in enumerate(lay.tables):
             rows = self.cache.table_rows(gi, rids, w)
             h[off: off + rr * w] = rows.reshape(-1)
-        fetch = getattr(self.rt.kernels, "fetch_ints", None) if self.on_cuda else None
-        if fetch is not None:
-            fetch(host, dev, lay.total)          # lay.total is a multiple of 4: every span is
-        else:
-            dev[: lay.total].copy_(host[: lay.total], non_blocking=True)
+        self.rt.kernels.fetch_ints(host, dev, lay.total)          # lay.total is a multiple of 4: every span is
         self.last_h2d_bytes = lay.total * 4
         if self._events[self._turn] is not None:
             self._events[self._turn].record()
@@ -309,14 +303,13 @@ class Stepper:
             static_ctx.memo.clear()
             graph = torch.cuda.CUDAGraph()
             k = self.rt.kernels
-            before = (getattr(k, "launches", 0), getattr(k, "library_calls", 0))
+            before = (k.launches, k.library_calls)
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             with torch.cuda.graph(graph, pool=self._graph_pool), self._pinned_stream():
                 out = self.model.forward(static_ctx, self.views)
-            counts = (getattr(k, "launches", 0) - before[0], getattr(k, "library_calls", 0) - before[1])
-            if hasattr(k, "launches"):
-                k.launches, k.library_calls = before          # capturing launched nothing
+            counts = (k.launches - before[0], k.library_calls - before[1])
+            k.launches, k.library_calls = before              # capturing launched nothing
             self._graphs[key] = (graph, out, self._dev, counts)
             return first
         graph, out, dev, counts = g
@@ -327,9 +320,8 @@ class Stepper:
         graph.replay()
         self.launched_graphs += 1
         k = self.rt.kernels
-        if hasattr(k, "launches"):
-            k.launches += counts[0]
-            k.library_calls += counts[1]
+        k.launches += counts[0]
+        k.library_calls += counts[1]
         return out
 
     def drop_graphs(self) -> None:

@@ -116,6 +116,8 @@ class CudaKernels:
 
     def __init__(self, device="cuda:0", head_dims=(), verbose: bool = True):
         self.device = torch.device(device)
+        if self.device.type == "cuda" and torch.cuda.is_available():
+            self.TARGET_BLOCKS = torch.cuda.get_device_properties(self.device).multi_processor_count
         jobs = core_jobs() + [attention_job(d) for d in sorted(set(head_dims))]
         for j in jobs:
             j["verbose"] = verbose
@@ -363,8 +365,8 @@ class CudaKernels:
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
             _DT[qkv.dtype], self._s()), "attention")
 
-    # Thread blocks of the deep shape that fit the GPU at once (2 per SM): the key range of every request is
-    # cut into so many splits that one wave of blocks covers the batch.
+    # Thread blocks of the deep shape that the key splits of a batch should fill: one per SM (set from the device's
+    # SM count when the kernels are loaded; 148 on a B200).
     TARGET_BLOCKS = 148
     MAX_SPLITS = 32
 

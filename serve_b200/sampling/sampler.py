@@ -53,11 +53,7 @@ class Sampler:
         feed_back = slots is not None and last_token is not None
         if feed_back:
             h[3, :n] = slots
-        fetch = getattr(self.kernels, "fetch_ints", None) if self._pin else None
-        if fetch is not None:
-            fetch(self._host, self._dev, self._host.numel())
-        else:
-            self._dev.copy_(self._host, non_blocking=True)
+        self.kernels.fetch_ints(self._host, self._dev, self._host.numel())
         if self._pin:
             if self._event is None:
                 self._event = torch.cuda.Event()

@@ -3,7 +3,8 @@ import json
 
 import pytest
 
-from serve_b200.config import ConfigError, LlamaConfig, build_spec, config_from_dict, known_architectures, load_config, load_preset
+from serve_b200.config import ConfigError, build_spec, config_from_dict, known_architectures, load_config, load_preset
+from serve_b200.config.llama import LlamaConfig
 from tests.helpers import TINY
 
 

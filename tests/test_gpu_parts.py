@@ -229,7 +229,6 @@ def _toy_plain(w, tokens, hidden):
 def test_toy_parts_are_registered_built_and_stepped():
     """A model made of parts defined in this file runs through the engine's step function, cut in portions and
     mixed with another request, and equals its plain whole-sequence version. No framework file knows these parts."""
-    from serve_b200.config.llama import LlamaConfig
     from serve_b200.weights.loader import load_from_source
     from serve_b200.weights.random_init import random_tensor
 
