@@ -3,11 +3,16 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 (2,048-token prompts, context limit
-4,096), timed on the device with CUDA events over K decode steps after W warm-up steps; ``e2e`` is the same
-through the Python entry point ``serve_b200.generate`` with token ids coming from and going back to the host
-every step; ``prefill`` is one 2,048-token prompt; ``points`` holds decode at batch 1 and 64; ``roofline``
+4,096), timed on the device with CUDA events over K decode steps after W warm-up steps; ``e2e`` is generated
+tokens per second of whole ``serve_b200.generate`` calls (8 requests of 2,048 prompt tokens and 256 new tokens; token
+ids come from and go back to the host every step; wall clock between synchronisations, one untimed call, the median
+of three: the way the reference's own benchmark times its generate()); ``prefill`` is one 2,048-token prompt;
+``points`` holds decode at batch 1 and 64; ``float32`` the decode step and the prefill in true 32-bit; ``roofline``
 compares the decode step with the bytes it has to read (every weight once, and the cache of the live requests).
 The weights (2.47 GB) are larger than the L2 cache, so no flush is needed between steps.
+
+``--impl reference`` runs limei1221/serve itself, unmodified, from baseline/_ref at the same configuration and prints
+the same line (baseline/reference_arm.py); it imports nothing of serve_b200.
 """
 import argparse
 import json

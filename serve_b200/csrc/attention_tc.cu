@@ -458,7 +458,7 @@ int encode4(CUtensorMap* map, const void* basep, const cuuint64_t dims[4], const
 SB_EXPORT int sb_attention_tc_supports(int H, int Hkv, int ps, int window, int q_stride) {
   if (H <= 0 || Hkv <= 0 || H % Hkv) return 0;
   const int G = H / Hkv;
-  if (G > 128 || (128 % G)) return 0;                   // a tile holds whole tokens: 128 / G of them
+  if (G > 128) return 0;                                // a tile holds whole tokens: 128 / G of them (rows beyond stay unused)
   if (ps < 8 || ps > BN || (BN % ps)) return 0;         // pages tile a stage of keys, in whole swizzle atoms
   if (window > 0) return 0;
   if (q_stride % 8) return 0;

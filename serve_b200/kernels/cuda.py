@@ -359,7 +359,9 @@ class CudaKernels:
         if qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
             return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
                                        page_size, scale, window, out, shape)
-        self.launches += 1
+        group = heads // kv_heads
+        # requests of at most 16 rows run in the decoding shape, the others in tiles: one launch each, as needed
+        self.launches += (1 if group <= 16 else 0) + (1 if group > 16 or shape.max_q * group > 16 else 0)
         _check(lib.sb_attention_simt(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,

@@ -5,9 +5,13 @@
     python -m serve_b200.kernels.microbench qkv_rope --m 2048 --k 2048 [--unfused]
     python -m serve_b200.kernels.microbench decode_attention --batch 64 --context 2176
     python -m serve_b200.kernels.microbench prefill_attention --tokens 2048
+    python -m serve_b200.kernels.microbench step --preset llama-3.2-3b --layers 8 --batches 1,8,32 --context 2048 --tokens 2048
 
 Each repetition uses another copy of the weights or of the cache (``--copies``), so that data comes from HBM and
 not from the L2 cache; with ``--graph`` the repetitions are captured in one CUDA graph, as decoding steps are.
+``step`` measures whole decoding steps (step function + sampling, from CUDA graphs) and a prompt step of a preset's
+shape with random weights, with fewer layers if asked, against the bytes and flops they need: the way to see how the
+engine does at other sizes, batches and contexts than the benchmark's.
 This is also the program the summaries under profiles/ were captured from (ncu -k ... python -m ...).
 """
 from __future__ import annotations
@@ -46,9 +50,91 @@ def _time(fn, reps, graph):
     return e0.elapsed_time(e1) * 1e3 / reps     # microseconds per call of fn
 
 
+def _step_bench(a) -> int:
+    """Decoding steps at several batch sizes and one prompt step, through the engine, for a preset's shape."""
+    import dataclasses
+    import json
+    import os
+
+    from ..config import EngineConfig, load_preset
+    from ..engine import Engine, StepEntry
+    from ..sampling import Sampler
+
+    hbm, flops_peak = 6540.5e9, 1669.7e12
+    peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.isfile(peaks):
+        with open(peaks) as f:
+            d = json.load(f)
+        hbm, flops_peak = float(d["hbm_gbs"]) * 1e9, float(d["bf16_tflops"]) * 1e12
+    full = load_preset(a.preset)
+    cfg = dataclasses.replace(full, num_hidden_layers=a.layers or full.num_hidden_layers)
+    h, nl, nh, nkv, d_, inter, v = (cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                    cfg.head_dim, cfg.intermediate_size, cfg.vocab_size)
+    per_layer = (nh + 2 * nkv) * d_ * h + h * nh * d_ + 3 * inter * h
+    weights, kv_per_token = (nl * per_layer + v * h) * 2, nl * 2 * nkv * d_ * 2
+    batches = [int(b) for b in a.batches.split(",")]
+    ctx, page = a.context, a.page_size
+    ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=max(batches) * (ctx + 256) // page + 64, max_slots=max(batches) + 2,
+                      max_tokens_per_step=max(min(ctx, 8192), a.tokens), max_context=ctx + 512, device=a.device)
+    out = {}
+    with torch.inference_mode():
+        eng = Engine.from_config(cfg, seed=0, engine_config=ec)
+        sampler = Sampler(eng.kernels, eng.rt.device, 0)
+        g = torch.Generator().manual_seed(1)
+        for b in batches:
+            rids = [f"b{b}-{i}" for i in range(b)]
+            for rid in rids:
+                done = 0
+                while done < ctx:
+                    n = min(ctx - done, ec.max_tokens_per_step)
+                    eng.step([StepEntry(rid, torch.randint(0, v, (n,), generator=g).tolist(), [])])
+                    done += n
+
+            def one():
+                logits = eng.step([StepEntry(rid, [7], [0]) for rid in rids])
+                return sampler.sample(logits, [0.0] * b, list(range(b)), [0] * b)
+
+            for _ in range(6):
+                one()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(a.reps * 4):
+                one()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / (a.reps * 4)
+            frac = (weights + b * (ctx + 6 + a.reps * 2) * kv_per_token) / (ms * 1e-3) / hbm
+            out[f"decode_b{b}"] = {"ms": round(ms, 3), "tokens_per_s": round(b * 1000 / ms, 1), "of_copy_bandwidth": round(frac, 3)}
+            for rid in rids:
+                eng.end(rid)
+        times = []
+        for _ in range(5):
+            toks = torch.randint(0, v, (a.tokens,), generator=g).tolist()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([StepEntry("p", toks, [a.tokens - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            eng.end("p")
+            times.append(e0.elapsed_time(e1))
+        ms = sorted(times[1:])[2]
+        t = a.tokens
+        flops = 2 * t * nl * per_layer + nl * 4 * d_ * nh * t * (t + 1) // 2 + 2 * v * h
+        out[f"prefill_{t}"] = {"ms": round(ms, 3), "tokens_per_s": round(t * 1000 / ms, 1),
+                               "of_cublas_burst": round(flops / (ms * 1e-3) / flops_peak, 3)}
+        eng.kernels.check_errors()
+    print(json.dumps({"preset": a.preset, "layers": nl, "layers_full": full.num_hidden_layers, "context": ctx, **out}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m serve_b200.kernels.microbench")
-    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention"])
+    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention", "step"])
+    ap.add_argument("--preset", default="llama-3.2-1b", help="step: the shape")
+    ap.add_argument("--layers", type=int, default=None, help="step: fewer layers than the preset has")
+    ap.add_argument("--batches", default="1,8,32", help="step: decoding batch sizes, comma separated")
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=2048)
     ap.add_argument("--k", type=int, default=2048)
@@ -67,6 +153,8 @@ def main(argv=None) -> int:
     ap.add_argument("--library", action="store_true", help="send products to the library (cuBLAS) instead of this engine's kernels")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
+    if a.kernel == "step":
+        return _step_bench(a)
     from .cuda import load_kernels
 
     dev = a.device

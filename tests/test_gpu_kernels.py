@@ -445,7 +445,7 @@ def test_attention_unwritten_cache_does_not_leak(K):
     torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 12, 16])
 @pytest.mark.parametrize("n,k", [(2048, 2048), (100, 64), (331, 96), (16, 8192), (4000, 32)])
 def test_skinny_linear(K, m, n, k):
     """The few-rows product against float64, bfloat16 and float outputs; and a row's result must not depend on
@@ -489,7 +489,7 @@ def test_fused_gate_up_equals_unfused(K, m, inter, k):
 
 
 def test_sizes_the_skinny_kernel_leaves_to_the_library(K):
-    for m, n, k in [(33, 64, 64), (4, 64, 120), (4, 64, 16)]:
+    for m, n, k in [(17, 64, 64), (33, 64, 64), (4, 64, 120), (4, 64, 16)]:
         assert K._core.sb_skinny_linear_supports(m, n, k, 0) == 0
         a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
         w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
@@ -678,6 +678,10 @@ TC_ATT_CASES = [
     (8, 8, 32, [130, 40], [130, 1000]),                    # no grouping
     (16, 2, 8, [65, 17], [400, 17]),                       # group of 8, small pages
     (64, 1, 64, [50], [777]),                              # group of 64: two tokens to a tile
+    (24, 8, 64, [300, 45], [300, 700]),                    # group of 3: 42 tokens (126 rows) to a tile, two rows unused
+    (10, 2, 32, [129, 90], [129, 500]),                    # group of 5
+    (12, 1, 16, [70], [333]),                              # group of 12: ten tokens to a tile
+    (100, 1, 64, [40], [40]),                              # group of 100: one token to a tile
 ]
 
 
