@@ -177,7 +177,7 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
     bool ok = key >= lo && key < hi;
     size_t off = 0;
     if (ok) {
-      const int blk = key / p.ps;
+      const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
       if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;
@@ -421,7 +421,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
     bool ok = key >= lo && key < hi;
     size_t off = 0;
     if (ok) {
-      const int blk = key / p.ps;
+      const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
       if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;

@@ -75,7 +75,7 @@ def _step_bench(a) -> int:
     batches = [int(b) for b in a.batches.split(",")]
     ctx, page = a.context, a.page_size
     ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=max(batches) * (ctx + 256) // page + 64, max_slots=max(batches) + 2,
-                      max_tokens_per_step=max(min(ctx, 8192), a.tokens), max_context=ctx + 512, device=a.device)
+                      max_tokens_per_step=max(min(ctx, 8192), a.tokens, max(batches)), max_context=ctx + 512, device=a.device)
     out = {}
     with torch.inference_mode():
         eng = Engine.from_config(cfg, seed=0, engine_config=ec)
