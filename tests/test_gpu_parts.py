@@ -117,113 +117,7 @@ def test_position_part_matches_plain_frequencies():
     torch.testing.assert_close(rot.inv_freq.cpu(), P.rope_inv_freq(32, 500000.0, dict(rope_type="llama3", **sc)), atol=0, rtol=2e-7)
 
 
-# ---- parts of other kinds, defined here, never part of any model of the framework ----------------------
-@register_part("mixer", "test_running_mean")
-class RunningMeanMixer(Mixer):
-    """A toy mixer with per-request state of fixed size: out_t = W * mean(h_0..h_t). State: sum [hidden] and count [1]."""
-
-    def __init__(self, spec, runtime):
-        super().__init__(spec, runtime)
-        self.hidden = int(spec.params["hidden"])
-        self.w = None
-
-    def tensor_decls(self):
-        return [TensorDecl(self.prefix + "mix.weight", (self.hidden, self.hidden))]
-
-    def load(self, tensors):
-        self.w = tensors[self.prefix + "mix.weight"]
-
-    def cache_need(self):
-        return CacheNeed(state_shape=(self.hidden + 1,))
-
-    def forward(self, h, ctx, cache):
-        if ctx.shape.pure_decode:
-            # one token per request: device-side indexing only, so that the step can be captured in a graph
-            slots = ctx.slots.long()
-            st = cache.state[slots]
-            sums = st[:, : self.hidden] + h.float()
-            counts = st[:, self.hidden] + 1
-            cache.state[slots] = torch.cat([sums, counts[:, None]], 1)
-            return ((sums / counts[:, None]) @ self.w.float().T).to(h.dtype)
-        out = torch.empty_like(h)
-        cu = ctx.cu_q.tolist()
-        for r, slot in enumerate(ctx.slots.tolist()):
-            a, b = cu[r], cu[r + 1]
-            st = cache.state[slot]
-            sums = st[: self.hidden] + torch.cumsum(h[a:b].float(), 0)
-            counts = st[self.hidden] + torch.arange(1, b - a + 1, device=h.device)
-            out[a:b] = ((sums / counts[:, None]) @ self.w.float().T).to(h.dtype)
-            st[: self.hidden] = sums[-1]
-            st[self.hidden] = counts[-1]
-        return out
-
-
-@register_part("feed_forward", "test_top1_experts")
-class Top1Experts(FeedForward):
-    """A toy routed feed-forward: router logits in float32, the best expert's matrix is applied."""
-
-    def __init__(self, spec, runtime):
-        super().__init__(spec, runtime)
-        self.hidden, self.experts = int(spec.params["hidden"]), int(spec.params["experts"])
-
-    def tensor_decls(self):
-        return [TensorDecl(self.prefix + "router.weight", (self.experts, self.hidden)),
-                TensorDecl(self.prefix + "experts.weight", (self.experts * self.hidden, self.hidden))]
-
-    def load(self, tensors):
-        self.router = tensors[self.prefix + "router.weight"]
-        self.w = tensors[self.prefix + "experts.weight"].view(self.experts, self.hidden, self.hidden)
-
-    def forward(self, h, ctx):
-        pick = (h.float() @ self.router.float().T).argmax(-1)
-        return torch.einsum("th,tch->tc", h.float(), self.w.float()[pick]).to(h.dtype)
-
-
-@register_part("position", "test_none_but_marker")
-class MarkerPosition(PositionEncoding):
-    """Another position encoding for the attention mixer: no rotation at all (rotary_dim 0)."""
-
-    def __init__(self, spec, runtime):
-        super().__init__(spec, runtime)
-        self.rotary_dim, self.pairing = 0, 0
-        self.inv_freq = torch.zeros(1, dtype=torch.float32, device=runtime.device)
-
-
-def _toy_spec(hidden, vocab):
-    norm = lambda p: PartSpec("rms", {"size": hidden, "eps": 1e-5}, prefix=p)
-    att = PartSpec("attention", {"hidden": hidden, "heads": 4, "kv_heads": 2, "head_dim": 16, "scale": None, "window": None,
-                                 "position": PartSpec("test_none_but_marker", {})}, prefix="l1.att.")
-    layers = [
-        LayerSpec.pre_norm(PartSpec("test_running_mean", {"hidden": hidden}, prefix="l0."),
-                  PartSpec("test_top1_experts", {"hidden": hidden, "experts": 3}, prefix="l0.moe."), norm("l0.n1."), norm("l0.n2.")),
-        LayerSpec.pre_norm(att, PartSpec("swiglu", {"hidden": hidden, "intermediate": 96}, prefix="l1.mlp."), norm("l1.n1."), norm("l1.n2.")),
-    ]
-    return ModelSpec("ToyForTests", hidden, vocab, PartSpec("table", {"vocab": vocab, "hidden": hidden, "name": "emb.weight"}),
-                     layers, [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)], norm("final."),
-                     PartSpec("linear", {"vocab": vocab, "hidden": hidden, "name": "head.weight", "tied_to": "emb.weight"}), 512)
-
-
-def _toy_plain(w, tokens, hidden):
-    """The same toy model, whole sequence, plain torch on the CPU."""
-    x = w["emb.weight"][tokens]
-    t = x.shape[0]
-    def mean_mix(h):
-        return (torch.cumsum(h, 0) / torch.arange(1, t + 1)[:, None]) @ w["l0.mix.weight"].T
-    def moe(h):
-        pick = (h @ w["l0.moe.router.weight"].T).argmax(-1)
-        return torch.einsum("th,tch->tc", h, w["l0.moe.experts.weight"].view(3, hidden, hidden)[pick])
-    def layer0(x):
-        x = x + mean_mix(P.rms_norm(x, w["l0.n1.weight"], 1e-5))
-        return x + moe(P.rms_norm(x, w["l0.n2.weight"], 1e-5))
-    x = layer0(x)
-    h = P.rms_norm(x, w["l1.n1.weight"], 1e-5)
-    q = (h @ w["l1.att.q_proj.weight"].T).view(t, 4, 16)
-    k = (h @ w["l1.att.k_proj.weight"].T).view(t, 2, 16)
-    v = (h @ w["l1.att.v_proj.weight"].T).view(t, 2, 16)
-    x = x + P.causal_attention(q, k, v, 0.25).reshape(t, 64) @ w["l1.att.o_proj.weight"].T
-    x = x + P.swiglu(P.rms_norm(x, w["l1.n2.weight"], 1e-5), w["l1.mlp.gate_proj.weight"], w["l1.mlp.up_proj.weight"], w["l1.mlp.down_proj.weight"])
-    x = layer0(x)
-    return P.rms_norm(x, w["final.weight"], 1e-5) @ w["emb.weight"].T
+from tests.toy_model import toy_plain as _toy_plain, toy_spec as _toy_spec  # noqa: E402  (also registers the toy parts)
 
 
 def test_toy_parts_are_registered_built_and_stepped():
@@ -397,3 +291,31 @@ def test_another_arrangement_and_a_windowed_layer_beside_a_full_one_generate_wit
     assert eng.last_stats.preemptions > 0
     eng.cache.check()
     assert eng.cache.live == 0 and all(g.pool.in_use == 0 for g in eng.cache.groups)
+
+
+def test_an_architecture_defined_in_the_tests_loads_from_a_folder_and_generates(tmp_path):
+    """The toy architecture of tests/toy_model.py (registered by that module alone) goes the whole way on the GPU: a model
+    folder written with seeded random weights, loaded by the architecture name in its config.json through the entry
+    point, greedy generation with portions of 16 tokens, against its plain whole-sequence version."""
+    from safetensors.torch import load_file
+
+    from serve_b200 import Request, generate, load_model
+    from serve_b200.weights import write_random_model
+    from tests.toy_model import ToyConfig
+
+    folder = str(tmp_path / "toy")
+    write_random_model(folder, ToyConfig(width=64, tokens=97), seed=5, std=0.3, norm_std=0.1, dtype=torch.float32)
+    w = {k: v.float() for k, v in load_file(folder + "/model.safetensors").items()}
+    eng, _ = load_model(folder, device="cuda", dtype="float32", page_size=8, num_pages=24, max_slots=3, max_tokens_per_step=32,
+                        prefill_chunk=16, max_context=128)
+    prompts = [helpers.random_tokens(97, 20, 1), helpers.random_tokens(97, 7, 2), helpers.random_tokens(97, 33, 3)]
+    want = []
+    for p in prompts:
+        toks = list(p)
+        for _ in range(6):
+            toks.append(int(_toy_plain(w, torch.tensor(toks), 64)[-1].argmax()))
+        want.append(toks[len(p):])
+    out = generate(eng, [Request(torch.tensor(p), len(p), 6) for p in prompts], temperature=0.0)
+    eng.kernels.check_errors()
+    assert [r.generated_tokens.tolist() for r in out] == want
+    assert eng.cache.live == 0
