@@ -6,6 +6,7 @@
     python -m serve_b200.kernels.microbench decode_attention --batch 64 --context 2176
     python -m serve_b200.kernels.microbench prefill_attention --tokens 2048
     python -m serve_b200.kernels.microbench step --preset llama-3.2-3b --layers 8 --batches 1,8,32 --context 2048 --tokens 2048
+    python -m serve_b200.kernels.microbench layer_run --preset llama-3.2-1b --batches 8,1 --context 2048
 
 Each repetition uses another copy of the weights or of the cache (``--copies``), so that data comes from HBM and
 not from the L2 cache; with ``--graph`` the repetitions are captured in one CUDA graph, as decoding steps are.
@@ -129,9 +130,56 @@ def _step_bench(a) -> int:
     return 0
 
 
+def _layer_run_phases(a) -> int:
+    """The persistent all-layers kernel (csrc/decode_stack.cu) on decoding steps of a preset's shape: what block 0's clock
+    says after every phase and every barrier of three of the layers."""
+    import dataclasses
+
+    from ..config import EngineConfig, load_preset
+    from ..engine import Engine, StepEntry
+
+    full = load_preset(a.preset)
+    cfg = dataclasses.replace(full, num_hidden_layers=a.layers or full.num_hidden_layers)
+    nl = cfg.num_hidden_layers
+    names = ["q/k/v", "barrier", "attention", "barrier", "o", "barrier", "gate/up", "barrier", "down", "barrier"]
+    with torch.inference_mode():
+        for batch in [int(b) for b in a.batches.split(",")]:
+            ec = EngineConfig(dtype="bfloat16", page_size=a.page_size, num_pages=batch * (a.context + 256) // a.page_size + 8,
+                              max_slots=batch + 1, max_tokens_per_step=max(2048, batch), max_context=a.context + 512,
+                              use_cuda_graphs=False, device=a.device)
+            eng = Engine.from_config(cfg, seed=0, engine_config=ec)
+            eng.kernels.use_layer_runs = True
+            g = torch.Generator().manual_seed(1)
+            rids = [f"r{i}" for i in range(batch)]
+            for rid in rids:
+                done = 0
+                while done < a.context:
+                    n = min(a.context - done, 2048)
+                    eng.step([StepEntry(rid, torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(), [])])
+                    done += n
+            timing = torch.zeros(nl * 10, dtype=torch.int64, device=a.device)
+            eng.kernels.layer_run_timing = timing
+            for i in range(6):
+                eng.step([StepEntry(rid, [5 + i], [0]) for rid in rids])
+            torch.cuda.synchronize()
+            eng.kernels.layer_run_timing = None
+            eng.kernels.use_layer_runs = False
+            eng.kernels.check_errors()
+            t = timing.view(nl, 10).cpu()
+            for layer in sorted({1, nl // 2, nl - 2} & set(range(1, nl))):
+                base = int(t[layer - 1, 9])
+                row = [int(t[layer, k]) for k in range(10)]
+                spans = [row[0] - base] + [row[k] - row[k - 1] for k in range(1, 10)]
+                print(f"batch {batch}, layer {layer}: {(row[9] - base) / 1000:.1f} us: " +
+                      ", ".join(f"{n} {s / 1000:.1f}" for n, s in zip(names, spans)))
+            del eng
+            torch.cuda.empty_cache()
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m serve_b200.kernels.microbench")
-    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention", "step"])
+    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention", "step", "layer_run"])
     ap.add_argument("--preset", default="llama-3.2-1b", help="step: the shape")
     ap.add_argument("--layers", type=int, default=None, help="step: fewer layers than the preset has")
     ap.add_argument("--batches", default="1,8,32", help="step: decoding batch sizes, comma separated")
@@ -155,6 +203,8 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     if a.kernel == "step":
         return _step_bench(a)
+    if a.kernel == "layer_run":
+        return _layer_run_phases(a)
     from .cuda import load_kernels
 
     dev = a.device
