@@ -137,16 +137,42 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
 
 // The decoding shape: requests that bring at most 16 / G tokens (G = H / Hkv query heads per kv head). One block per
 // (request, kv head); the G heads of every token are rows of one tile, so a key or value is fetched once for the
-// whole group. The 8 warps deal the keys out among themselves; a warp's
-// lanes share the head's elements, a score is a shuffle-tree sum of fixed order, and every warp keeps its own
-// running maximum, sum and output for up to DEC_ROWS rows at a time (more rows: more passes over the keys); a warp
-// takes KU consecutive keys per step (warp w: keys lo + w KU .. lo + w KU + KU - 1, then 8 KU further on). The
-// warps' results meet in shared memory and are merged in warp order. Same recurrences as above, base e, full-
-// precision expf.
+// whole group. LPK lanes share a key (each holds EPL <= 16 elements of the head vector), so a warp works on
+// KPW = 32 / LPK keys at a time and a score costs log2(LPK) shuffles; the 8 warps x KPW lane groups are 8 KPW
+// independent streams over the keys (stream s takes keys lo + s, lo + s + 8 KPW, ...), each with its own running
+// maximum, sum and output for up to DEC_ROWS rows at a time (more rows: more passes over the keys). The streams meet
+// in shared memory and are merged in stream order. Same recurrences as above, base e, full-precision expf.
 constexpr int DEC_WARPS = 8;
 constexpr int DEC_ROWS = 4;
-constexpr int DPL = (D + 31) / 32;   // elements of a head vector per lane
-constexpr int KU = DPL <= 2 ? 8 : (DPL <= 4 ? 4 : 2);   // keys a warp asks for at a time
+constexpr int LPK = D <= 16 ? 1 : (D <= 32 ? 2 : (D <= 64 ? 4 : (D <= 128 ? 8 : 16)));
+constexpr int NCH = D / 4;                         // a head vector in chunks of four elements
+constexpr int CPL = (NCH + LPK - 1) / LPK;         // chunks per lane: lane `sub` of a key's lanes takes chunks sub, sub + LPK, ...
+constexpr int EPL = CPL * 4;                       // so neighbouring lanes read neighbouring 16 bytes of a key
+constexpr int KPW = 32 / LPK;
+constexpr int DEC_STREAMS = DEC_WARPS * KPW;
+static_assert(D % 4 == 0 && EPL <= 16, "at most 16 elements of a head vector per lane");
+
+__device__ __forceinline__ void load4(const float* p, float* x) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* x) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x), b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+  x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+}
+
+// element e of lane `sub` is element dec_index(sub, e) of the head vector
+__device__ __forceinline__ int dec_index(int sub, int e) { return ((e >> 2) * LPK + sub) * 4 + (e & 3); }
+
+template <typename T>
+__device__ __forceinline__ void dec_load(const T* __restrict__ base, size_t off, int sub, bool there, float (&x)[EPL]) {
+#pragma unroll
+  for (int c = 0; c < CPL; ++c) {
+    if (there && c * LPK + sub < NCH) load4(base + off + (size_t)(c * LPK + sub) * 4, &x[c * 4]);
+    else { x[c * 4] = 0.f; x[c * 4 + 1] = 0.f; x[c * 4 + 2] = 0.f; x[c * 4 + 3] = 0.f; }
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
@@ -154,9 +180,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
     int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out) {
   extern __shared__ float smem[];
-  float* Qs = smem;                                                                          // [16][D]
-  float (*Om)[DEC_ROWS][D] = reinterpret_cast<float (*)[DEC_ROWS][D]>(Qs + 16 * D);          // [DEC_WARPS][DEC_ROWS][D]
-  float (*MLm)[DEC_ROWS][2] = reinterpret_cast<float (*)[DEC_ROWS][2]>(Qs + 16 * D + DEC_WARPS * DEC_ROWS * D);
+  float* Qs = smem;                                        // [16][D]
+  float* Om = Qs + 16 * D;                                 // [DEC_STREAMS][DEC_ROWS][LPK * EPL]
+  float* MLm = Om + DEC_STREAMS * DEC_ROWS * LPK * EPL;    // [DEC_STREAMS][DEC_ROWS][2]
   const int r = blockIdx.y, hk = blockIdx.x;
   const int q0 = cu_q[r], qn = cu_q[r + 1] - q0;
   const int G = H / Hkv;
@@ -165,6 +191,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
   const int L = kv_len[r];
   const int p0 = L - qn;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gk = lane / LPK, sub = lane - gk * LPK;
+  const int stream = warp * KPW + gk;
   for (int w = tid; w < M * D; w += DEC_WARPS * 32) {
     const int row = w / D, d = w - row * D;
     const int tok = row / G, hd = hk * G + (row - tok * G);
@@ -173,7 +201,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
   __syncthreads();
   const int* bt = block_table + (size_t)r * bt_width;
   for (int m0 = 0; m0 < M; m0 += DEC_ROWS) {
-    float q[DEC_ROWS][DPL], acc[DEC_ROWS][DPL], m_run[DEC_ROWS], l_run[DEC_ROWS];
+    float q[DEC_ROWS][EPL], acc[DEC_ROWS][EPL], m_run[DEC_ROWS], l_run[DEC_ROWS];
     int pos[DEC_ROWS];
 #pragma unroll
     for (int i = 0; i < DEC_ROWS; ++i) {
@@ -182,82 +210,76 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
       m_run[i] = -INFINITY;
       l_run[i] = 0.f;
 #pragma unroll
-      for (int e = 0; e < DPL; ++e) {
-        const int d = lane + 32 * e;
-        q[i][e] = (valid && d < D) ? Qs[(m0 + i) * D + d] : 0.f;
+      for (int e = 0; e < EPL; ++e) {
+        q[i][e] = (valid && dec_index(sub, e) < D) ? Qs[(m0 + i) * D + dec_index(sub, e)] : 0.f;
         acc[i][e] = 0.f;
       }
     }
     const int last_row = min(m0 + DEC_ROWS, M) - 1;
     const int lo = window > 0 ? max(0, p0 + m0 / G - window + 1) : 0;
     const int hi = p0 + last_row / G + 1;             // exclusive; <= L
-    // KU keys at a time, their table entries, keys and values asked for together: one trip to memory per KU keys
-    for (int key0 = lo + warp * KU; key0 < hi; key0 += DEC_WARPS * KU) {
-      size_t off[KU];
-      bool there[KU];
+    // this stream's keys: lo + stream, then DEC_STREAMS further on; the next key's loads go out before this key's sums
+    auto locate = [&](int key, size_t& off) -> bool {
+      if (key >= hi) return false;
+      const int blk = key / ps;
+      const int page = blk < bt_width ? bt[blk] : -1;
+      if (page < 0 || page >= num_pages) return false;          // (a missing page: nothing to read)
+      off = (((size_t)page * Hkv + hk) * ps + (key - blk * ps)) * D;
+      return true;
+    };
+    float kn[EPL], vn[EPL];
+    size_t off = 0;
+    int key = lo + stream;
+    bool there = locate(key, off);
+    dec_load(kc, off, sub, there, kn);
+    dec_load(vc, off, sub, there, vn);
+    for (int base = lo; base < hi; base += DEC_STREAMS) {
+      float kv[EPL], vv[EPL];
 #pragma unroll
-      for (int j = 0; j < KU; ++j) {
-        const int key = key0 + j;
-        const int blk = key / ps;
-        const int page = (key < hi && blk < bt_width) ? bt[blk] : -1;
-        there[j] = page >= 0 && page < num_pages;           // (a missing page: nothing to read; warp-uniform)
-        off[j] = there[j] ? (((size_t)page * Hkv + hk) * ps + (key - blk * ps)) * D : 0;
-      }
-      float kv[KU][DPL], vv[KU][DPL];
+      for (int e = 0; e < EPL; ++e) { kv[e] = kn[e]; vv[e] = vn[e]; }
+      const int this_key = key;
+      const bool this_there = there;
+      key += DEC_STREAMS;
+      there = locate(key, off);
+      dec_load(kc, off, sub, there, kn);
+      dec_load(vc, off, sub, there, vn);
 #pragma unroll
-      for (int j = 0; j < KU; ++j)
+      for (int i = 0; i < DEC_ROWS; ++i) {
+        float sc = 0.f;
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) {
-          const int d = lane + 32 * e;
-          kv[j][e] = (there[j] && d < D) ? to_float(kc[off[j] + d]) : 0.f;
-          vv[j][e] = (there[j] && d < D) ? to_float(vc[off[j] + d]) : 0.f;
-        }
+        for (int e = 0; e < EPL; ++e) sc += q[i][e] * kv[e];
 #pragma unroll
-      for (int j = 0; j < KU; ++j) {
-        const int key = key0 + j;
-        if (!there[j]) continue;
+        for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+        const bool ok = this_there && this_key <= pos[i] && (window <= 0 || this_key > pos[i] - window);
+        if (ok) {
+          const float m_new = fmaxf(m_run[i], sc);
+          const float alpha = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - m_new);
+          const float pr = expf(sc - m_new);
+          l_run[i] = l_run[i] * alpha + pr;
 #pragma unroll
-        for (int i = 0; i < DEC_ROWS; ++i) {
-          float sc = 0.f;
-#pragma unroll
-          for (int e = 0; e < DPL; ++e) sc += q[i][e] * kv[j][e];
-          sc = warp_sum(sc);
-          const bool ok = key <= pos[i] && (window <= 0 || key > pos[i] - window);
-          if (ok) {
-            const float m_new = fmaxf(m_run[i], sc);
-            const float alpha = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - m_new);
-            const float pr = expf(sc - m_new);
-            l_run[i] = l_run[i] * alpha + pr;
-#pragma unroll
-            for (int e = 0; e < DPL; ++e) acc[i][e] = acc[i][e] * alpha + pr * vv[j][e];
-            m_run[i] = m_new;
-          }
+          for (int e = 0; e < EPL; ++e) acc[i][e] = acc[i][e] * alpha + pr * vv[e];
+          m_run[i] = m_new;
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < DEC_ROWS; ++i) {
 #pragma unroll
-      for (int e = 0; e < DPL; ++e) {
-        const int d = lane + 32 * e;
-        if (d < D) Om[warp][i][d] = acc[i][e];
-      }
-      if (lane == 0) { MLm[warp][i][0] = m_run[i]; MLm[warp][i][1] = l_run[i]; }
+      for (int e = 0; e < EPL; ++e) Om[((size_t)stream * DEC_ROWS + i) * (LPK * EPL) + dec_index(sub, e)] = acc[i][e];
+      if (sub == 0) { MLm[(stream * DEC_ROWS + i) * 2] = m_run[i]; MLm[(stream * DEC_ROWS + i) * 2 + 1] = l_run[i]; }
     }
     __syncthreads();
     for (int w = tid; w < DEC_ROWS * D; w += DEC_WARPS * 32) {
       const int i = w / D, d = w - i * D;
       if (m0 + i >= M) continue;
       float mm = -INFINITY;
-#pragma unroll
-      for (int wv = 0; wv < DEC_WARPS; ++wv) mm = fmaxf(mm, MLm[wv][i][0]);
+      for (int st = 0; st < DEC_STREAMS; ++st) mm = fmaxf(mm, MLm[(st * DEC_ROWS + i) * 2]);
       float ll = 0.f, o = 0.f;
-#pragma unroll
-      for (int wv = 0; wv < DEC_WARPS; ++wv) {
-        const float mw = MLm[wv][i][0];
+      for (int st = 0; st < DEC_STREAMS; ++st) {
+        const float mw = MLm[(st * DEC_ROWS + i) * 2];
         const float f = (mw == -INFINITY) ? 0.f : expf(mw - mm);
-        ll += MLm[wv][i][1] * f;
-        o += Om[wv][i][d] * f;
+        ll += MLm[(st * DEC_ROWS + i) * 2 + 1] * f;
+        o += Om[((size_t)st * DEC_ROWS + i) * (LPK * EPL) + d] * f;
       }
       const int row = m0 + i, tok = row / G, hd = hk * G + (row - tok * G);
       out[(size_t)(q0 + tok) * H * D + (size_t)hd * D + d] = from_float<T>(ll > 0.f ? o / ll : 0.f);
@@ -284,7 +306,7 @@ SB_EXPORT int sb_attention_simt(const void* qkv, int q_stride, const void* kc, c
   const bool tiles_needed = !decode_shape || (long long)max_q * G > 16;
   dim3 grid((max_q + BM - 1) / BM, H, n_rows);
   dim3 dgrid(Hkv, n_rows);
-  const size_t dsmem = (size_t)(16 * D + DEC_WARPS * DEC_ROWS * D + DEC_WARPS * DEC_ROWS * 2) * sizeof(float);
+  const size_t dsmem = (size_t)(16 * D + DEC_STREAMS * DEC_ROWS * LPK * EPL + DEC_STREAMS * DEC_ROWS * 2) * sizeof(float);
   if (dtype == SB_DTYPE_F32) {
     if (tiles_needed) {
       auto k = attention_simt_kernel<float>;

@@ -248,8 +248,9 @@ int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cuda
 // The same product in true 32-bit arithmetic (plain fused multiply-adds, no tensor-core mode), for the float32 path's
 // decoding steps: a warp owns NC output columns and MB activation rows, its lanes share K out among themselves in
 // steps of four values, partial sums meet by a shuffle tree of fixed order. The weights are read once from memory at
-// streaming speed; the activation rows come from the L1 cache. A row's result does not depend on the other rows.
-constexpr int F32_NC = 4, F32_MB = 8, F32_WARPS = 8;
+// streaming speed (KU steps' loads per column go out together); the activation rows come from the L1 cache. NC is chosen
+// so that there are blocks for every SM (narrow outputs: one column a warp). A row's result does not depend on the other rows.
+constexpr int F32_MB = 8, F32_WARPS = 8;
 
 __device__ __forceinline__ float4 ld_stream_f4(const float* p) {
   float4 v;
@@ -257,58 +258,68 @@ __device__ __forceinline__ float4 ld_stream_f4(const float* p) {
   return v;
 }
 
+template <int NC, int KU>
 __global__ void __launch_bounds__(F32_WARPS * 32, 2) skinny_linear_f32_kernel(const float* __restrict__ a, const float* __restrict__ w,
                                                                                float* __restrict__ out, int M, int N, int K) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int n0 = (blockIdx.x * F32_WARPS + warp) * F32_NC;
+  const int n0 = (blockIdx.x * F32_WARPS + warp) * NC;
   const int m0 = blockIdx.y * F32_MB;
-  const float* wp[F32_NC];
+  const float* wp[NC];
   const float* ap[F32_MB];
 #pragma unroll
-  for (int c = 0; c < F32_NC; ++c) wp[c] = w + (size_t)min(n0 + c, N - 1) * K;      // clamped: computed and dropped
+  for (int c = 0; c < NC; ++c) wp[c] = w + (size_t)min(n0 + c, N - 1) * K;      // clamped: computed and dropped
 #pragma unroll
   for (int i = 0; i < F32_MB; ++i) ap[i] = a + (size_t)min(m0 + i, M - 1) * K;
-  float acc[F32_NC][F32_MB];
+  float acc[NC][F32_MB];
 #pragma unroll
-  for (int c = 0; c < F32_NC; ++c)
+  for (int c = 0; c < NC; ++c)
 #pragma unroll
     for (int i = 0; i < F32_MB; ++i) acc[c][i] = 0.f;
   // the weights do not depend on the kernel before this one: their first loads go out before the wait
-  float4 wv[F32_NC];
-  int k = lane * 4;
-  if (k < K && n0 < N) {
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 wv[KU][NC];
+  const int k_first = lane * 4;
 #pragma unroll
-    for (int c = 0; c < F32_NC; ++c) wv[c] = ld_stream_f4(wp[c] + k);
-  }
+  for (int u = 0; u < KU; ++u)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) wv[u][c] = (k_first + u * 128 < K && n0 < N) ? ld_stream_f4(wp[c] + k_first + u * 128) : zero4;
   pdl_launch_dependents();
   pdl_wait();
   if (n0 >= N) return;
-  for (; k < K; k += 128) {
-    float4 wn[F32_NC];
-    const int kn = k + 128;
-    if (kn < K) {
+  for (int k = k_first; k < K; k += 128 * KU) {
+    float4 wn[KU][NC];
 #pragma unroll
-      for (int c = 0; c < F32_NC; ++c) wn[c] = ld_stream_f4(wp[c] + kn);
-    }
-    float4 av[F32_MB];
+    for (int u = 0; u < KU; ++u)
 #pragma unroll
-    for (int i = 0; i < F32_MB; ++i) av[i] = __ldg(reinterpret_cast<const float4*>(ap[i] + k));
-#pragma unroll
-    for (int c = 0; c < F32_NC; ++c)
-#pragma unroll
-      for (int i = 0; i < F32_MB; ++i) {
-        acc[c][i] = fmaf(wv[c].x, av[i].x, acc[c][i]);
-        acc[c][i] = fmaf(wv[c].y, av[i].y, acc[c][i]);
-        acc[c][i] = fmaf(wv[c].z, av[i].z, acc[c][i]);
-        acc[c][i] = fmaf(wv[c].w, av[i].w, acc[c][i]);
+      for (int c = 0; c < NC; ++c) {
+        const int kn = k + 128 * KU + u * 128;
+        wn[u][c] = kn < K ? ld_stream_f4(wp[c] + kn) : zero4;
       }
-    if (kn < K) {
 #pragma unroll
-      for (int c = 0; c < F32_NC; ++c) wv[c] = wn[c];
+    for (int u = 0; u < KU; ++u) {
+      const int ku = k + u * 128;
+      if (ku < K) {
+        float4 av[F32_MB];
+#pragma unroll
+        for (int i = 0; i < F32_MB; ++i) av[i] = __ldg(reinterpret_cast<const float4*>(ap[i] + ku));
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+          for (int i = 0; i < F32_MB; ++i) {
+            acc[c][i] = fmaf(wv[u][c].x, av[i].x, acc[c][i]);
+            acc[c][i] = fmaf(wv[u][c].y, av[i].y, acc[c][i]);
+            acc[c][i] = fmaf(wv[u][c].z, av[i].z, acc[c][i]);
+            acc[c][i] = fmaf(wv[u][c].w, av[i].w, acc[c][i]);
+          }
+      }
     }
+#pragma unroll
+    for (int u = 0; u < KU; ++u)
+#pragma unroll
+      for (int c = 0; c < NC; ++c) wv[u][c] = wn[u][c];
   }
 #pragma unroll
-  for (int c = 0; c < F32_NC; ++c)
+  for (int c = 0; c < NC; ++c)
 #pragma unroll
     for (int i = 0; i < F32_MB; ++i) {
       const float s = warp_sum(acc[c][i]);
@@ -328,13 +339,24 @@ SB_EXPORT int sb_skinny_linear_f32_supports(int M, int N, int K) {
 SB_EXPORT int sb_skinny_linear_f32(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
   if (!sb_skinny_linear_f32_supports(M, N, K)) return SB_ERR_SHAPE;
   if (!aligned16(a) || !aligned16(w)) return SB_ERR_ALIGN;
-  const dim3 grid((N + F32_WARPS * F32_NC - 1) / (F32_WARPS * F32_NC), (M + F32_MB - 1) / F32_MB);
-  SB_PDL_CHECK(launch_pdl(skinny_linear_f32_kernel, grid, dim3(F32_WARPS * 32), 0, stream, (const float*)a, (const float*)w,
-                          (float*)out, M, N, K));
+  const int mt = (M + F32_MB - 1) / F32_MB;
+  const int want = 2 * sm_count();                     // two blocks fit an SM
+  const float *af = (const float*)a, *wf = (const float*)w;
+  float* of = (float*)out;
+  // columns per warp: as many as still leave blocks for every SM
+  if ((long long)((N + F32_WARPS * 4 - 1) / (F32_WARPS * 4)) * mt >= want) {
+    SB_PDL_CHECK(launch_pdl(skinny_linear_f32_kernel<4, 1>, dim3((N + F32_WARPS * 4 - 1) / (F32_WARPS * 4), mt), dim3(F32_WARPS * 32), 0,
+                            stream, af, wf, of, M, N, K));
+  } else if ((long long)((N + F32_WARPS * 2 - 1) / (F32_WARPS * 2)) * mt >= want) {
+    SB_PDL_CHECK(launch_pdl(skinny_linear_f32_kernel<2, 2>, dim3((N + F32_WARPS * 2 - 1) / (F32_WARPS * 2), mt), dim3(F32_WARPS * 32), 0,
+                            stream, af, wf, of, M, N, K));
+  } else {
+    SB_PDL_CHECK(launch_pdl(skinny_linear_f32_kernel<1, 4>, dim3((N + F32_WARPS - 1) / F32_WARPS, mt), dim3(F32_WARPS * 32), 0, stream,
+                            af, wf, of, M, N, K));
+  }
   return 0;
 }
 
-// 1 if sb_skinny_linear takes these sizes, else 0 (the caller then uses the library product).
 // Up to 16 rows (one tile of the 16-row operand). A second tile of rows was measured on the Llama-3.2-1B shapes
 // against the library, in a graph: 17..32 rows took 9.4 / 5.2 / 14.4 us (q/k/v, output, down projection) against
 // 5.9 / 5.1 / 12.9 us, and 32 us against 15 for gate/up, because every block re-reads all activation rows; at 12..16
