@@ -7,12 +7,15 @@
     python -m serve_b200.kernels.microbench prefill_attention --tokens 2048
     python -m serve_b200.kernels.microbench step --preset llama-3.2-3b --layers 8 --batches 1,8,32 --context 2048 --tokens 2048
     python -m serve_b200.kernels.microbench layer_run --preset llama-3.2-1b --batches 8,1 --context 2048
+    python -m serve_b200.kernels.microbench marginal --preset llama-3.2-1b --batches 8,1 --context 2048
 
 Each repetition uses another copy of the weights or of the cache (``--copies``), so that data comes from HBM and
 not from the L2 cache; with ``--graph`` the repetitions are captured in one CUDA graph, as decoding steps are.
 ``step`` measures whole decoding steps (step function + sampling, from CUDA graphs) and a prompt step of a preset's
 shape with random weights, with fewer layers if asked, against the bytes and flops they need: the way to see how the
 engine does at other sizes, batches and contexts than the benchmark's.
+``marginal`` times the same decoding steps with one kind of kernel left out at a time (the step's results are then
+wrong; only its time is read): what each kernel costs inside the chain, hand-overs included, against its bytes.
 This is also the program the summaries under profiles/ were captured from (ncu -k ... python -m ...).
 """
 from __future__ import annotations
@@ -130,6 +133,76 @@ def _step_bench(a) -> int:
     return 0
 
 
+def _marginal_times(a) -> int:
+    """Decoding steps with one kind of kernel left out at a time: the difference to the whole step is what that kernel
+    costs where it stands, between its neighbours."""
+    import dataclasses
+    import json
+
+    from ..config import EngineConfig, load_preset
+    from ..engine import Engine, StepEntry
+    from ..sampling import Sampler
+
+    full = load_preset(a.preset)
+    cfg = dataclasses.replace(full, num_hidden_layers=a.layers or full.num_hidden_layers)
+    v, hidden = cfg.vocab_size, cfg.hidden_size
+    batches = [int(b) for b in a.batches.split(",")]
+    ctx, page = a.context, a.page_size
+
+    def leave_out(kernels, what):
+        """Shadow one method of the kernels object (which engines share) by a do-nothing; returns the shadowed name."""
+        nothing = lambda *args, **kw: None
+        name = {"norm": "add_rmsnorm", "attention": "attention", "q/k/v": "qkv_rope_cache", "gate/up": "gate_up_swiglu"}.get(what, "linear")
+        if name == "linear":
+            whole = kernels.linear
+
+            def linear(x, w, out):
+                kind = "head" if w.shape[0] == v else ("down projection" if x.shape[1] > hidden else "output projection")
+                return None if kind == what else whole(x, w, out)
+
+            nothing = linear
+        setattr(kernels, name, nothing)
+        return name
+
+    out = {}
+    kinds = ["nothing", "norm", "q/k/v", "attention", "output projection", "gate/up", "down projection", "head"]
+    with torch.inference_mode():
+        for what in kinds:
+            ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=max(batches) * (ctx + 256) // page + 64,
+                              max_slots=max(batches) + 2, max_tokens_per_step=max(min(ctx, 8192), max(batches)), max_context=ctx + 512,
+                              device=a.device)
+            eng = Engine.from_config(cfg, seed=0, engine_config=ec)
+            sampler = Sampler(eng.kernels, eng.rt.device, 0)
+            g = torch.Generator().manual_seed(1)
+            for b in batches:
+                rids = [f"b{b}-{i}" for i in range(b)]
+                for rid in rids:
+                    eng.step([StepEntry(rid, torch.randint(0, v, (ctx,), generator=g).tolist(), [])])
+                shadowed = leave_out(eng.kernels, what) if what != "nothing" else None
+
+                def one():
+                    logits = eng.step([StepEntry(rid, [7], [0]) for rid in rids])
+                    return sampler.sample(logits, [0.0] * b, list(range(b)), [0] * b)
+
+                try:
+                    ms = _time(lambda: [one() for _ in range(4)], a.reps, False) / 4e3
+                finally:
+                    if shadowed:
+                        delattr(eng.kernels, shadowed)       # the class's method shows again
+                out.setdefault(f"b{b}", {})[what] = round(ms, 4)
+                for rid in rids:
+                    eng.end(rid)
+            eng.kernels.check_errors()
+            del eng, sampler
+    for b, row in out.items():
+        whole = row["nothing"]
+        print(f"{a.preset}, {cfg.num_hidden_layers} layers, context {ctx}, {b}: whole step {whole * 1e3:.1f} us; left out -> us less a step "
+              f"(a layer): " + ", ".join(f"{k} {(whole - t) * 1e3:.1f}" + ("" if k == "head" else f" ({(whole - t) * 1e3 / cfg.num_hidden_layers:.2f})")
+                                       for k, t in row.items() if k != "nothing"))
+    print(json.dumps(out))
+    return 0
+
+
 def _layer_run_phases(a) -> int:
     """The persistent all-layers kernel (csrc/decode_stack.cu) on decoding steps of a preset's shape: what block 0's clock
     says after every phase and every barrier of three of the layers."""
@@ -179,7 +252,7 @@ def _layer_run_phases(a) -> int:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m serve_b200.kernels.microbench")
-    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention", "step", "layer_run"])
+    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention", "step", "layer_run", "marginal"])
     ap.add_argument("--preset", default="llama-3.2-1b", help="step: the shape")
     ap.add_argument("--layers", type=int, default=None, help="step: fewer layers than the preset has")
     ap.add_argument("--batches", default="1,8,32", help="step: decoding batch sizes, comma separated")
@@ -205,6 +278,8 @@ def main(argv=None) -> int:
         return _step_bench(a)
     if a.kernel == "layer_run":
         return _layer_run_phases(a)
+    if a.kernel == "marginal":
+        return _marginal_times(a)
     from .cuda import load_kernels
 
     dev = a.device
