@@ -62,7 +62,9 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
   constexpr int NW = GU ? 2 : 1;
   constexpr int NB = NW * NT;                        // 8-column tiles of w rows a lane streams
   constexpr int BN = 8 * NT;                         // output columns per block
-  constexpr int UNROLL = (MT * NB > 1) ? 4 : 8;      // groups of 32 k-values whose loads are issued together
+  // groups of 32 k-values whose loads are issued together: 8 where the registers allow it (one or, with at most 8 rows,
+  // two tiles of w: at hidden 2048 a warp's whole share of q/k/v or of the output projection is then asked for before the wait)
+  constexpr int UNROLL = (MT * NB > 2 || (MT * NB > 1 && !HALF)) ? 4 : 8;
   __shared__ float red[WARPS][NB][MT][16 * 8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, tq = lane & 3;
