@@ -343,8 +343,11 @@ def main():
     pk = peaks()
     page = 64
     max_batch = max(64, args.batch)
+    # the scheduler's token budget per step: all prompts of the end-to-end batch in one step (8 x 2,048), as a server sized
+    # for this load would be set; the 2,048-token prompt step and the decoding steps are what they are under any budget
+    step_tokens = max(args.batch * PROMPT_LEN, PREFILL_TOKENS)
     ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=max_batch * CONTEXT // page + 64, max_slots=max_batch + 2,
-                      max_tokens_per_step=max(PROMPT_LEN, PREFILL_TOKENS), max_context=CONTEXT,
+                      max_tokens_per_step=step_tokens, max_context=CONTEXT,
                       use_cuda_graphs=not args.no_graphs)
     with torch.inference_mode():
         eng = Engine.from_config(cfg, seed=0, engine_config=ec)
@@ -397,7 +400,7 @@ def main():
         "config": {"model": "llama-3.2-1b-shape", "layers": cfg.num_hidden_layers, "layers_full": cfg_full.num_hidden_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": page,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": page, "step_tokens": step_tokens,
                    "parallelism": "single-gpu", "l2": "inputs larger than L2: 2.47 GB of weights read per step",
                    "peaks": pk["source"]},
         "e2e": e2e,
