@@ -196,6 +196,12 @@ class CudaKernels:
     # The tensor-memory product works in 128 x 256 tiles, one CTA per SM: with fewer tiles than this most SMs
     # would idle and the library's split-k kernels are the better choice.
     TCGEN05_MIN_TILES = 96
+    # A product without an epilogue of its own (output and down projection) goes to the library at every row count above the
+    # few-rows kernel's: measured on a B200 at the 1B shapes from 128 to 4,096 rows the library is the faster one (2,048
+    # rows: 14.9 against 16.2 us and 47.5 against 52.3 us; 3,072 rows: 20.7 / 26.9 and 69.7 / 95.9), and a prompt step of
+    # 2,048 / 4,096 / 8,192 tokens went from 4.48 / 8.94 / 23.3 to 4.31 / 8.46 / 20.9 ms. The tiles earn their place where
+    # an epilogue is fused (gate/up + SwiGLU, q/k/v + rotation + cache write). True: plain products use the tiles too (tests).
+    tcgen05_for_plain_products = False
 
     def _tcgen05_worthwhile(self, m: int, n_acc: int) -> bool:
         return self.use_tcgen05 and (-(-m // 128)) * (-(-n_acc // 256)) >= self.TCGEN05_MIN_TILES
@@ -243,14 +249,14 @@ class CudaKernels:
         if a.dtype != w.dtype or a.shape[1] != w.shape[1] or out.shape[0] != a.shape[0] or out.shape[1] != w.shape[0]:
             raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} do not fit")
         m, n, k = a.shape[0], w.shape[0], a.shape[1]
-        key = (a.dtype, out.dtype, m, n, k, self.use_skinny_linear, self.use_tcgen05, self.TCGEN05_MIN_TILES, 0)
+        key = (a.dtype, out.dtype, m, n, k, self.use_skinny_linear, self.use_tcgen05, self.TCGEN05_MIN_TILES, self.tcgen05_for_plain_products, 0)
         route = self._routes.get(key)
         if route is None:
             route = 0
             if a.dtype == torch.bfloat16 and self.use_skinny_linear and self._core.sb_skinny_linear_supports(m, n, k, 0):
                 route = 1
-            elif (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self._tcgen05_worthwhile(m, n)
-                    and self._core.sb_gemm_tcgen05_supports(m, n, k, 0)):
+            elif (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and self.tcgen05_for_plain_products
+                    and self._tcgen05_worthwhile(m, n) and self._core.sb_gemm_tcgen05_supports(m, n, k, 0)):
                 route = 2
             elif (a.dtype == torch.float32 and out.dtype == torch.float32 and self.use_skinny_linear
                     and self._core.sb_skinny_linear_f32_supports(m, n, k)):

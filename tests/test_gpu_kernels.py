@@ -505,8 +505,10 @@ TC_SHAPES = [(128, 128, 64), (256, 256, 256), (2048, 3072, 2048), (300, 264, 200
 def cta_mode(K, request):
     """Tiles of more than 128 rows run on CTA pairs (cta_group::2) by default; "single" keeps them on the one-CTA kernel."""
     K._core.sb_gemm_tcgen05_use_pairs(2 if request.param == "pairs" else 0)
+    K.tcgen05_for_plain_products = True      # (plain products are the library's unless asked for: these tests ask)
     yield request.param
     K._core.sb_gemm_tcgen05_use_pairs(1)
+    del K.tcgen05_for_plain_products
 
 
 @pytest.mark.parametrize("m,n,k", TC_SHAPES + [(257, 520, 136), (4096, 512, 64), (777, 2048, 1000)])

@@ -70,9 +70,11 @@ def test_benchmark_widths_match_plain(big, dtype):
     if dtype == "bfloat16":
         assert eng.stepper.launched_graphs >= 10
         assert eng.kernels.launches > launches_before
-        # the whole-prompt step keeps its products on this engine's kernels (only the mixed steps' 65..131-row
-        # products go to the library)
-        assert eng.kernels.library_calls - library_before < 40
+        # the whole-prompt step keeps its fused products (q/k/v with rotation, gate/up with SwiGLU) on this engine's
+        # kernels and sends the two plain ones of a layer to the library; the four mixed steps' 17..131-row products are
+        # all the library's; decoding steps use none
+        layers = CFG["num_hidden_layers"]
+        assert 2 * layers <= eng.kernels.library_calls - library_before <= (2 + 4 * 4) * layers
 
 
 SMALL = dict(CFG, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=512)
@@ -96,13 +98,18 @@ def test_many_rows_decoding_from_graphs_through_the_tensor_memory_products(tmp_p
     eng = Engine.from_folder(folder, EngineConfig(dtype="bfloat16", page_size=16, num_pages=n_req * 3, max_slots=n_req,
                                                   max_tokens_per_step=1024, max_context=64, use_cuda_graphs=True))
     eng.kernels.TCGEN05_MIN_TILES = 1
+    eng.kernels.tcgen05_for_plain_products = True
     steps = [{"step": 0, "entries": [{"id": rid, "tokens": toks[:-decoded], "want": [len(toks) - decoded - 1]} for rid, toks in reqs.items()],
               "end": []}]
     for d in range(decoded):
         steps.append({"step": d + 1, "entries": [{"id": rid, "tokens": [toks[len(toks) - decoded + d]], "want": [0]}
                                                   for rid, toks in reqs.items()], "end": []})
-    with torch.inference_mode():
-        got = helpers.replay(eng, steps)
+    try:
+        with torch.inference_mode():
+            got = helpers.replay(eng, steps)
+    finally:
+        del eng.kernels.TCGEN05_MIN_TILES, eng.kernels.tcgen05_for_plain_products     # (engines share the kernels object)
+        eng.kernels._routes.clear()
     eng.kernels.check_errors()
     assert eng.stepper.launched_graphs >= decoded - 1
     scale = max(float(p.abs().max()) for p in plain.values())

@@ -60,6 +60,7 @@ def test_random_configuration(tmp_path, seed, dtype, tensor_memory_products):
                                                       use_cuda_graphs=True))
         if tensor_memory_products:
             eng.kernels.TCGEN05_MIN_TILES = 1
+            eng.kernels.tcgen05_for_plain_products = True
         eng.kernels._routes.clear()
         try:
             for v in eng.stepper.views:          # a page that is read before it is written shows
@@ -75,4 +76,5 @@ def test_random_configuration(tmp_path, seed, dtype, tensor_memory_products):
         finally:
             if tensor_memory_products:
                 del eng.kernels.TCGEN05_MIN_TILES
+                del eng.kernels.tcgen05_for_plain_products
             eng.kernels._routes.clear()
