@@ -234,13 +234,10 @@ class CacheManager:
             return [nb] * len(self.groups)
         return [max(0, nb - r.reserved[gi]) for gi in range(len(self.groups))]
 
-    def fits(self, batch: Sequence[Tuple[Hashable, int]], freed: Sequence[Hashable] = (), at_most: Optional[int] = None) -> bool:
-        """Would ``reserve(batch)`` succeed once the requests in ``freed`` were closed? Changes nothing.
-        ``at_most``: an upper bound the caller knows for the pages any group can want (a request that grows by n
-        tokens wants at most ceil(n / page_size)); if even that many are free, nothing is counted."""
+    def free_after(self, batch: Sequence[Tuple[Hashable, int]], freed: Sequence[Hashable] = ()) -> List[int]:
+        """Per group: pages that would be left (negative: missing) after ``reserve(batch)``, once the requests in
+        ``freed`` were closed. Changes nothing."""
         n_groups = len(self.groups)
-        if at_most is not None and all(at_most <= g.pool.available for g in self.groups):
-            return True
         free = [g.pool.available for g in self.groups]
         gone = set()
         for rid in freed:
@@ -261,7 +258,15 @@ class CacheManager:
                     d = nb - r.reserved[gi]
                     if d > 0:
                         free[gi] -= d
-        return all(f >= 0 for f in free)
+        return free
+
+    def fits(self, batch: Sequence[Tuple[Hashable, int]], freed: Sequence[Hashable] = (), at_most: Optional[int] = None) -> bool:
+        """Would ``reserve(batch)`` succeed once the requests in ``freed`` were closed? Changes nothing.
+        ``at_most``: an upper bound the caller knows for the pages any group can want (a request that grows by n
+        tokens wants at most ceil(n / page_size)); if even that many are free, nothing is counted."""
+        if at_most is not None and all(at_most <= g.pool.available for g in self.groups):
+            return True
+        return all(f >= 0 for f in self.free_after(batch, freed))
 
     def reserve(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
         """Give every listed request pages up to its new length, or raise OutOfPages and change nothing."""

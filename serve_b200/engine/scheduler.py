@@ -28,7 +28,7 @@ from typing import Deque, Dict, List, Optional, Sequence
 from .step import FROM_DEVICE
 
 
-@dataclass
+@dataclass(eq=False)      # a request is itself, not its fields: `in` and `remove` on the queues compare identities
 class SchedRequest:
     rid: int
     prompt: List[int]
@@ -173,9 +173,8 @@ class Scheduler:
         running requests already take in this step, as (request, length after the step) pairs."""
         entries: List[PlannedEntry] = []
         free_slots = self.cache.free_slots + len(self.evicted)
-        freed = [v.rid for v in self.evicted]
-        batch = list(batch)
         pools = self.cache.pool_pages()
+        free = None           # per group: pages left once the running requests have theirs (asked for at the first candidate)
         while self.waiting and left > 0 and free_slots > 0:
             r = self.waiting[0]
             if r in self.evicted:
@@ -187,14 +186,17 @@ class Scheduler:
                 if self.running and any(have + p > self.admission_fraction * pool
                                         for have, p, pool in zip(self.promised, promise, pools)):
                     break
-            if not self.cache.fits(batch + [(r.rid, r.fed + take)], freed=freed):
+            if free is None:
+                free = self.cache.free_after(batch, freed=[v.rid for v in self.evicted])
+            want = self.cache.pages_wanted(r.rid, r.fed + take)
+            if any(w > f for w, f in zip(want, free)):
                 break
+            free = [f - w for f, w in zip(free, want)]
             if self.reserve_full:
                 self.promised = [a + b for a, b in zip(self.promised, promise)]
             self.waiting.popleft()
             self.running.append(r)
             entries.append(PlannedEntry(r, r.pending()[:take], take == n))
-            batch.append((r.rid, r.fed + take))
             left -= take
             free_slots -= 1
         return entries

@@ -136,6 +136,8 @@ class CudaKernels:
         self.use_tcgen05 = True             # tests: False keeps many-row products in the library
         self.fuse_rope = True               # tests: False runs the rotary kernel after the q/k/v product
         self.use_tcgen05_attention = True   # tests: False keeps prompt portions on the mma.sync kernel
+        if os.environ.get("SERVE_B200_TCGEN05_PLAIN") == "1":     # measurements: plain products on the tiles too
+            self.tcgen05_for_plain_products = True
         self._stream_handle = None           # set by on_current_stream(): the stream every launch goes to
         self._routes: Dict[tuple, int] = {}  # which product kernel takes a shape (asked of the libraries once)
         self._tc_attention_ok: Dict[tuple, bool] = {}
