@@ -198,6 +198,12 @@ class CacheManager:
     def slot(self, rid: Hashable) -> int:
         return self._requests[rid].slot
 
+    def lengths_and_slots(self, rids: Sequence[Hashable]) -> Tuple[List[int], List[int]]:
+        """(tokens held, state slot) of each listed request, in one pass (a step asks this of every request it has)."""
+        requests = self._requests
+        found = [requests[rid] for rid in rids]
+        return [r.length for r in found], [r.slot for r in found]
+
     @property
     def free_slots(self) -> int:
         return len(self._free_slots)
@@ -313,6 +319,16 @@ class CacheManager:
                 g.table[r.slot, r.released[gi]: first] = -1
                 r.released[gi] = first
 
+    def commit_many(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
+        """``commit`` for every (request, new length) of a step."""
+        if self._windowed:
+            for rid, new_len in batch:
+                self.commit(rid, new_len)
+            return
+        requests = self._requests
+        for rid, new_len in batch:
+            requests[rid].length = new_len
+
     def close(self, rid: Hashable) -> None:
         r = self._requests.pop(rid)
         for gi, g in enumerate(self.groups):
@@ -322,10 +338,13 @@ class CacheManager:
         self._free_slots.append(r.slot)
 
     # ---- step inputs ----------------------------------------------------
-    def table_rows(self, group: int, rids: Sequence[Hashable], width: Optional[int] = None) -> np.ndarray:
-        """[len(rids), width] int32 block-table rows (width: blocks of the longest listed request)."""
+    def table_rows(self, group: int, rids: Sequence[Hashable], width: Optional[int] = None,
+                   slots: Optional[Sequence[int]] = None) -> np.ndarray:
+        """[len(rids), width] int32 block-table rows (width: blocks of the longest listed request). ``slots``: the
+        requests' slots, if the caller has them already."""
         g = self.groups[group]
-        slots = [self._requests[rid].slot for rid in rids]
+        if slots is None:
+            slots = [self._requests[rid].slot for rid in rids]
         if width is None:
             width = max([self._requests[rid].reserved[group] for rid in rids] + [1])
         return np.ascontiguousarray(g.table[slots, :width])

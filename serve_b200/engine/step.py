@@ -130,38 +130,45 @@ class Stepper:
 
     # ---- the step -----------------------------------------------------------
     def plan(self, entries: Sequence[StepEntry]):
-        """Validate a batch and reserve its pages (raises OutOfPages, changing nothing)."""
+        """Validate a batch and reserve its pages (raises OutOfPages, changing nothing). Returns what the step needs of
+        every request, each a list in the order of the entries: (batch of (request, length after the step), request
+        ids, tokens brought, tokens held before, state slots, number of wanted places)."""
         if not entries:
             raise ValueError("a step needs at least one entry")
-        seen = set()
-        batch = []
-        total = 0
-        for e in entries:
-            seen.add(e.rid)
+        rids, q_lens = [], []
+        total = n_want = 0
+        for e in entries:                        # one pass: a step may have a thousand entries
             n = len(e.tokens)
             if n == 0:
                 raise ValueError(f"request {e.rid!r} brings no tokens")
-            for w in e.want:
-                if not (0 <= w < n):
-                    raise ValueError(f"request {e.rid!r} wants place {w} of {n} tokens")
+            want = e.want
+            if want:
+                for w in want:
+                    if not (0 <= w < n):
+                        raise ValueError(f"request {e.rid!r} wants place {w} of {n} tokens")
+                n_want += len(want)
             total += n
-        if len(seen) != len(entries):
+            rids.append(e.rid)
+            q_lens.append(n)
+        if len(set(rids)) != len(rids):
             raise ValueError("a request appears twice in one step")
         if total > self.max_tokens_per_step:
             raise ValueError(f"the step holds {total} tokens; the limit is {self.max_tokens_per_step}")
+        cache = self.cache
         opened = []
         try:
-            for e in entries:
-                if not self.cache.is_open(e.rid):
-                    self.cache.open(e.rid)
-                    opened.append(e.rid)
-                batch.append((e.rid, self.cache.length(e.rid) + len(e.tokens)))
-            self.cache.reserve(batch)
+            for rid in rids:
+                if not cache.is_open(rid):
+                    cache.open(rid)
+                    opened.append(rid)
+            starts, slots = cache.lengths_and_slots(rids)
+            batch = [(rid, have + n) for rid, have, n in zip(rids, starts, q_lens)]
+            cache.reserve(batch)
         except Exception:
             for rid in opened:
-                self.cache.close(rid)
+                cache.close(rid)
             raise
-        return batch
+        return batch, rids, q_lens, starts, slots, n_want
 
     def _undo_plan(self, batch) -> None:
         """A step that is refused after its pages were reserved gives back requests it had just opened."""
@@ -171,20 +178,17 @@ class Stepper:
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch; returns [wanted, vocab] float32 logits (None if nothing is wanted)."""
-        batch = self.plan(entries)
+        batch, rids, q_lens, starts, slots, n_want = self.plan(entries)
         r = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
-        starts = [self.cache.length(e.rid) for e in entries]
         new_lens = [n for _, n in batch]
         t = sum(q_lens)
-        n_want = sum(len(e.want) for e in entries)
-        pure_decode = all(q == 1 for q in q_lens)
+        pure_decode = t == r                     # every entry brings at least one token
         graphable = self.use_cuda_graphs and pure_decode and n_want == r and r <= 512
-        rids = [e.rid for e in entries]
+        longest = max(new_lens)
         if graphable:
             widths = [self.cache.max_blocks for _ in self.cache.groups]
         else:
-            widths = [max(self.cache.blocks_for(n) for n in new_lens) for _ in self.cache.groups]
+            widths = [self.cache.blocks_for(longest) for _ in self.cache.groups]
         lay = _Layout(t, r, n_want, widths)
         host, dev = self._buffers(lay.total)
         h = host.numpy()
@@ -210,7 +214,7 @@ class Stepper:
         vocab = self.model.spec.vocab_size
         if toks.min() < 0:
             # FROM_DEVICE becomes -(slot + 1): the embedding kernel then reads the slot's last sampled token
-            slot_of = np.asarray([self.cache.slot(rid) for rid in rids], dtype=np.int64)[row_of]
+            slot_of = np.asarray(slots, dtype=np.int64)[row_of]
             toks = np.where(toks == FROM_DEVICE, -(slot_of + 1), np.where(toks < 0, vocab, toks))
         if toks.max() >= vocab:
             self._undo_plan(batch)
@@ -220,7 +224,7 @@ class Stepper:
         h[row_o: row_o + t] = row_of
         h[cu_o: cu_o + r + 1] = cu
         h[kv_o: kv_o + r] = new_lens
-        h[sl_o: sl_o + r] = [self.cache.slot(rid) for rid in rids]
+        h[sl_o: sl_o + r] = slots
         rq_o, _ = lay.spans["rows_by_q"]
         if pure_decode:
             h[rq_o: rq_o + r] = row_of
@@ -235,7 +239,7 @@ class Stepper:
             else:
                 h[lr_o: lr_o + n_want] = [int(cu[i]) + w for i, e in enumerate(entries) for w in e.want]
         for gi, (off, rr, w) in enumerate(lay.tables):
-            rows = self.cache.table_rows(gi, rids, w)
+            rows = self.cache.table_rows(gi, rids, w, slots=slots)
             h[off: off + rr * w] = rows.reshape(-1)
         self.rt.kernels.fetch_ints(host, dev, lay.total)          # lay.total is a multiple of 4: every span is
         self.last_h2d_bytes = lay.total * 4
@@ -248,7 +252,7 @@ class Stepper:
 
         ctx = StepContext(
             rt=self.rt,
-            shape=BatchShape(r, t, max(q_lens), min(q_lens), max(new_lens), pure_decode,
+            shape=BatchShape(r, t, max(q_lens), min(q_lens), longest, pure_decode,
                              rows_by_q=view("rows_by_q") if neg_q_sorted is not None else None, neg_q_sorted=neg_q_sorted),
             tokens=view("tokens"), positions=view("positions"), token_row=view("token_row"),
             cu_q=view("cu_q"), kv_len=view("kv_len"), slots=view("slots"), logit_rows=view("logit_rows"),
@@ -257,12 +261,11 @@ class Stepper:
         )
         self.last_slots = ctx.slots
         if graphable:
-            logits = self._run_graph(ctx, r, max(new_lens))
+            logits = self._run_graph(ctx, r, longest)
         else:
             with self._pinned_stream():
                 logits = self.model.forward(ctx, self.views)
-        for rid, n in batch:
-            self.cache.commit(rid, n)
+        self.cache.commit_many(batch)
         return logits
 
     # ---- CUDA graphs for pure-decode steps ------------------------------------

@@ -157,9 +157,25 @@ def _generate_loop(model, requests, sched, sampler, stop, return_logits, timelin
                     inflight = None
                     continue
                 raise RuntimeError("the scheduler found nothing to run although requests are waiting")
-            entries = [StepEntry(p.request.rid, p.tokens, [len(p.tokens) - 1] if p.samples else []) for p in planned]
+            # one pass over the step's requests (a thousand of them in a full step) for everything that is per request
+            entries, sampling, temps, sampled_rids, idxs = [], [], [], [], []
+            n_dec = n_tok = 0
+            for p in planned:
+                r, toks = p.request, p.tokens
+                n = len(toks)
+                n_tok += n
+                if p.samples:
+                    entries.append(StepEntry(r.rid, toks, [n - 1]))
+                    sampling.append(r)
+                    temps.append(r.temperature)
+                    sampled_rids.append(r.rid)
+                    made = len(r.generated)
+                    idxs.append(made)
+                    if n == 1 and made:
+                        n_dec += 1
+                else:
+                    entries.append(StepEntry(r.rid, toks, []))
             logits = model.step(entries)
-            sampling = [p.request for p in planned if p.samples]
             host = event = None
             if sampling:
                 turn ^= 1
@@ -167,17 +183,14 @@ def _generate_loop(model, requests, sched, sampler, stop, return_logits, timelin
                     staging[turn] = torch.empty(max(64, 1 << (len(sampling) - 1).bit_length()), dtype=torch.int32, pin_memory=on_cuda)
                 host = staging[turn]
                 # on a GPU the sampling kernel writes the tokens straight into this pinned host buffer
-                out = sampler.sample(logits, [r.temperature for r in sampling], [r.rid for r in sampling],
-                                     [len(r.generated) for r in sampling], [model.cache.slot(r.rid) for r in sampling],
+                out = sampler.sample(logits, temps, sampled_rids, idxs, model.cache.lengths_and_slots(sampled_rids)[1],
                                      model.stepper.last_token, out=host if on_cuda else None)
                 if on_cuda:
                     event = torch.cuda.Event()
                     event.record()
                 else:
                     host[: len(sampling)].copy_(out)
-            n_dec = sum(1 for p in planned if len(p.tokens) == 1 and p.samples and p.request.generated)
-            stamp = (sum(len(p.tokens) for p in planned) - n_dec, n_dec, model.stepper.last_h2d_bytes + 16 * len(sampling))
-            idxs = [len(r.generated) for r in sampling]
+            stamp = (n_tok - n_dec, n_dec, model.stepper.last_h2d_bytes + 16 * len(sampling))
             done = sched.update(planned, [None] * len(sampling))
             if done:
                 rows = {id(r): i for i, r in enumerate(sampling)}
