@@ -272,6 +272,7 @@ def main(argv=None) -> int:
     ap.add_argument("--legacy-attention", action="store_true", help="prompt attention on the mma.sync kernel instead of tcgen05")
     ap.add_argument("--unfused", action="store_true", help="qkv_rope: the product, then the rotary kernel")
     ap.add_argument("--library", action="store_true", help="send products to the library (cuBLAS) instead of this engine's kernels")
+    ap.add_argument("--tiles", action="store_true", help="send products of more than 16 rows to the tcgen05 tiles whatever their size")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
     if a.kernel == "step":
@@ -286,6 +287,9 @@ def main(argv=None) -> int:
     K = load_kernels(dev, head_dims=(a.head_dim,))
     if a.library:
         K.use_tcgen05 = K.use_skinny_linear = False
+    if a.tiles:
+        K.TCGEN05_MIN_TILES = 1
+        K.tcgen05_for_plain_products = True
     if a.legacy_attention:
         K.use_tcgen05_attention = False
     bf = torch.bfloat16
