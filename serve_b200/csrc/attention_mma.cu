@@ -735,7 +735,7 @@ SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_
 
 // which: bit 0 launch the wide shape (for the n_wide requests listed in wide_rows if that is given, else for all:
 // a step of hundreds of decoding requests and a few prompt portions then launches blocks for the portions only),
-// bit 1 launch the deep shape. With num_splits > 1 the deep shape needs
+// bit 1 launch the deep shape, bit 3 see below. With num_splits > 1 the deep shape needs
 // ``scratch`` (sb_attention_mma_scratch_bytes) and merges either in the block that finishes last (tickets: n_rows * Hkv
 // ints, zero before the first launch; every launch leaves them zero) or, with tickets == nullptr, in a second kernel.
 SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
@@ -780,7 +780,8 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
     // Very many (request, kv head) pairs, as in a large batch of short requests: one warp per pair. Seven such
     // blocks share an SM, so the fixed part of a pair's time (table, queries, first loads, store) overlaps with
     // six other pairs' key loops instead of being paid once per four-warp block.
-    const bool crowd = num_splits == 1 && (long long)n_rows * Hkv >= 1024;
+    // (bit 3 of ``which``: the caller, who knows that the contexts are short, asks for it from fewer pairs on.)
+    const bool crowd = num_splits == 1 && ((long long)n_rows * Hkv >= 1024 || ((which & 8) && (long long)n_rows * Hkv >= 768));
     int rc = roomy ? launch_deep<false, 8>(p, n_rows, stream)
                    : (crowd ? launch_deep<false, 1>(p, n_rows, stream) : launch_deep<false, 4>(p, n_rows, stream));
     if (rc) return rc;
