@@ -14,6 +14,9 @@
 // second product, as the reference does (serve/kernels/attn_prefill.py:71, attn_decode.py:110). The
 // recurrences are those of attn_prefill.py:58-72 with exp2 and a folded log2(e) (attn_prefill.py:330-331).
 // Compile with -DSB_HEAD_DIM=<multiple of 16, 16..256>.
+#include <algorithm>
+#include <type_traits>
+
 #include "common.cuh"
 
 #ifndef SB_HEAD_DIM
@@ -780,14 +783,31 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
     // Very many (request, kv head) pairs, as in a large batch of short requests: one warp per pair. Seven such
     // blocks share an SM, so the fixed part of a pair's time (table, queries, first loads, store) overlaps with
     // six other pairs' key loops instead of being paid once per four-warp block.
-    // (bit 3 of ``which``: the caller, who knows that the contexts are short, asks for it from fewer pairs on.)
-    const bool crowd = num_splits == 1 && ((long long)n_rows * Hkv >= 1024 || ((which & 8) && (long long)n_rows * Hkv >= 768));
-    int rc = roomy ? launch_deep<false, 8>(p, n_rows, stream)
-                   : (crowd ? launch_deep<false, 1>(p, n_rows, stream) : launch_deep<false, 4>(p, n_rows, stream));
+    // Blocks between those sizes: four warps, two or three blocks an SM at head_dim 64. Two cases where blocks of two
+    // warps (five an SM) do better, because all of them are on the SMs at once: (a) bit 3 of ``which``, the caller knows
+    // that no sequence is longer than 1,024 tokens: a block's time is then mostly its fixed part (90 requests x 8 kv
+    // heads of 512 tokens: 20.3 against 25.5 us); one warp per pair then pays from where two-warp blocks no longer fit
+    // at once; (b) the last round of four-warp blocks would be under 70 % full (40 requests x 8 kv heads are 296 + 24
+    // blocks: 35.2 against 42.8 us at 2,048 tokens, 63.7 against 78.2 at 4,096).
+    const long long pairs = (long long)n_rows * Hkv, blocks = pairs * num_splits;
+    const bool short_ctx = (which & 8) != 0;
+    auto at_once = [&](int nw) { return (long long)sm_count() * (long long)std::max<size_t>(1, (227 * 1024) / (deep_smem_bytes(nw) + 2048)); };
+    const long long cap4 = at_once(4), cap2 = at_once(2);
+    const bool crowd = num_splits == 1 && (pairs >= 1024 || (short_ctx && pairs > cap2));
+    const long long rounds4 = (blocks + cap4 - 1) / cap4;
+    const bool thin_last_round = blocks * 10 < rounds4 * cap4 * 7;
+    const bool pairs_of_warps = !roomy && !crowd && blocks > cap4 && blocks <= cap2 && (short_ctx || thin_last_round);
+    auto launch = [&](auto upper) -> int {
+      constexpr bool U = decltype(upper)::value;
+      if (roomy) return launch_deep<U, 8>(p, n_rows, stream);
+      if (crowd) return launch_deep<U, 1>(p, n_rows, stream);
+      if (pairs_of_warps) return launch_deep<U, 2>(p, n_rows, stream);
+      return launch_deep<U, 4>(p, n_rows, stream);
+    };
+    int rc = launch(std::false_type{});
     if (rc) return rc;
     if (which & 4) {
-      rc = roomy ? launch_deep<true, 8>(p, n_rows, stream)
-                 : (crowd ? launch_deep<true, 1>(p, n_rows, stream) : launch_deep<true, 4>(p, n_rows, stream));
+      rc = launch(std::true_type{});
       if (rc) return rc;
     }
     if (num_splits > 1 && tickets == nullptr) {

@@ -411,9 +411,10 @@ class CudaKernels:
         split_size, num_splits, scratch, tickets = 64, 1, None, None
         if which & 2:
             num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
-            if num_splits == 1 and shape.max_kv <= 1024:
-                # short contexts: one warp per (request, kv head) pays from 768 pairs on (measured at 960 pairs: 13.5
-                # against 20.1 us at 192 tokens, 28.1 against 32.1 at 512, but 95 against 90 at 2,048)
+            if shape.max_kv <= 1024:
+                # short contexts: blocks of fewer warps, so that all of them are on the SMs at once (measured at 960
+                # (request, kv head) pairs, one warp each: 13.5 against 20.1 us at 192 tokens, 28.1 against 32.1 at 512,
+                # but 95 against 90 at 2,048; at 320 to 720 pairs, two warps each: csrc/attention_mma.cu)
                 which |= 8
             if num_splits > 1:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
