@@ -738,12 +738,12 @@ SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_
 
 // which: bit 0 launch the wide shape (for the n_wide requests listed in wide_rows if that is given, else for all:
 // a step of hundreds of decoding requests and a few prompt portions then launches blocks for the portions only),
-// bit 1 launch the deep shape, bit 3 see below. With num_splits > 1 the deep shape needs
+// bit 1 launch the deep shape. ``longest``: no sequence of the step is longer (0: not known). With num_splits > 1 the deep shape needs
 // ``scratch`` (sb_attention_mma_scratch_bytes) and merges either in the block that finishes last (tickets: n_rows * Hkv
 // ints, zero before the first launch; every launch leaves them zero) or, with tickets == nullptr, in a second kernel.
 SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
                                const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
-                               void* out, int n_rows, int max_q, int which, int split_size, int num_splits, void* scratch,
+                               void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
                                int* tickets, const int* wide_rows, int n_wide, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
@@ -755,7 +755,7 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
-  p.split_size = split_size; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+  p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = wide_rows; p.heads_in_x = 0;
   if (which & 1) {
     auto k = attention_wide_kernel;
@@ -780,28 +780,38 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
     // bit 2 of ``which``: some request has more than 8 rows (the caller knows the largest token count).
     // Few blocks (at most one per SM): 8 warps each, so that an SM still has warps to switch between.
     const bool roomy = (long long)n_rows * Hkv * num_splits <= sm_count() && deep_smem_bytes(8) <= 227 * 1024;
-    // Very many (request, kv head) pairs, as in a large batch of short requests: one warp per pair. Seven such
-    // blocks share an SM, so the fixed part of a pair's time (table, queries, first loads, store) overlaps with
-    // six other pairs' key loops instead of being paid once per four-warp block.
-    // Blocks between those sizes: four warps, two or three blocks an SM at head_dim 64. Two cases where blocks of two
-    // warps (five an SM) do better, because all of them are on the SMs at once: (a) bit 3 of ``which``, the caller knows
-    // that no sequence is longer than 1,024 tokens: a block's time is then mostly its fixed part (90 requests x 8 kv
-    // heads of 512 tokens: 20.3 against 25.5 us); one warp per pair then pays from where two-warp blocks no longer fit
-    // at once; (b) the last round of four-warp blocks would be under 70 % full (40 requests x 8 kv heads are 296 + 24
-    // blocks: 35.2 against 42.8 us at 2,048 tokens, 63.7 against 78.2 at 4,096).
+    // Otherwise the block shape follows from what fits the SMs at once (two four-warp blocks an SM at head_dim 64, five
+    // two-warp blocks, ten one-warp blocks) and from how long the sequences can be (``longest``, 0 if the caller does
+    // not say). A block's fixed part (table, queries, first loads, merge, store) is 4-5 us: it should overlap with
+    // other blocks' key loops, and a round of blocks that is mostly empty costs a whole block's time. Measured with 8 kv
+    // heads of 64 (`profiles/steps_other_sizes_and_contexts.md`):
+    //  - four warps while one round of them holds all blocks, for very long sequences, and for a few hundred pairs of
+    //    1,024 to 4,096 tokens whose last round is not thin (64 requests x 2,048 tokens: 48.4 us against 49.5 with two);
+    //  - one warp per pair only for a thousand and more pairs of at most 256 tokens (1,000 requests x 192: 76.9 us
+    //    against 84.1 with two warps and 135.6 with four); with longer sequences one-warp blocks lose badly (192
+    //    requests x 2,048: 176 us against 137 with two warps);
+    //  - two warps otherwise (90 requests x 512: 21.0 against 25.5 us with four; 40 x 2,048, where four-warp blocks are
+    //    296 + 24: 35.2 against 42.8), unless their own last round would be thin and one-warp blocks fit at once
+    //    (100 requests x 300 tokens: 17.1 us with one warp, 20.2 with two).
     const long long pairs = (long long)n_rows * Hkv, blocks = pairs * num_splits;
-    const bool short_ctx = (which & 8) != 0;
     auto at_once = [&](int nw) { return (long long)sm_count() * (long long)std::max<size_t>(1, (227 * 1024) / (deep_smem_bytes(nw) + 2048)); };
-    const long long cap4 = at_once(4), cap2 = at_once(2);
-    const bool crowd = num_splits == 1 && (pairs >= 1024 || (short_ctx && pairs > cap2));
-    const long long rounds4 = (blocks + cap4 - 1) / cap4;
-    const bool thin_last_round = blocks * 10 < rounds4 * cap4 * 7;
-    const bool pairs_of_warps = !roomy && !crowd && blocks > cap4 && blocks <= cap2 && (short_ctx || thin_last_round);
+    const long long cap4 = at_once(4), cap2 = at_once(2), cap1 = at_once(1);
+    auto thin_last_round = [&](long long cap) {          // the last round of blocks would be under 70 % full
+      const long long rounds = (blocks + cap - 1) / cap;
+      return blocks * 10 < rounds * cap * 7;
+    };
+    int warps = 2;
+    if (roomy) warps = 8;
+    else if (blocks <= cap4) warps = 4;
+    else if (num_splits == 1 && pairs >= 1024 && longest > 0 && longest <= 256) warps = thin_last_round(cap1) ? 2 : 1;
+    else if (longest <= 0 || longest >= 4096) warps = (thin_last_round(cap4) && blocks <= cap2) ? 2 : 4;
+    else if (longest > 1024 && blocks <= 2 * cap4 && !thin_last_round(cap4)) warps = 4;
+    else if (num_splits == 1 && longest <= 1024 && blocks > cap2 && blocks <= cap1 && thin_last_round(cap2)) warps = 1;
     auto launch = [&](auto upper) -> int {
       constexpr bool U = decltype(upper)::value;
-      if (roomy) return launch_deep<U, 8>(p, n_rows, stream);
-      if (crowd) return launch_deep<U, 1>(p, n_rows, stream);
-      if (pairs_of_warps) return launch_deep<U, 2>(p, n_rows, stream);
+      if (warps == 8) return launch_deep<U, 8>(p, n_rows, stream);
+      if (warps == 1) return launch_deep<U, 1>(p, n_rows, stream);
+      if (warps == 2) return launch_deep<U, 2>(p, n_rows, stream);
       return launch_deep<U, 4>(p, n_rows, stream);
     };
     int rc = launch(std::false_type{});

@@ -408,14 +408,9 @@ class CudaKernels:
         if (which & 1) and neg_q is not None and getattr(shape, "rows_by_q", None) is not None:
             n_wide = bisect.bisect_left(neg_q, -(16 // group) if group <= 16 else 0)
             wide_rows = shape.rows_by_q
-        split_size, num_splits, scratch, tickets = 64, 1, None, None
+        num_splits, scratch, tickets = 1, None, None
         if which & 2:
             num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
-            if shape.max_kv <= 1024:
-                # short contexts: blocks of fewer warps, so that all of them are on the SMs at once (measured at 960
-                # (request, kv head) pairs, one warp each: 13.5 against 20.1 us at 192 tokens, 28.1 against 32.1 at 512,
-                # but 95 against 90 at 2,048; at 320 to 720 pairs, two warps each: csrc/attention_mma.cu)
-                which |= 8
             if num_splits > 1:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
@@ -434,7 +429,7 @@ class CudaKernels:
         _check(lib.sb_attention_mma(
             _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-            which, split_size, num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, self._s()), "attention")
+            which, int(shape.max_kv), num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, self._s()), "attention")
 
     def _tc_attention_takes(self, lib, heads, kv_heads, head_dim, page_size, window, stride) -> bool:
         key = (heads, kv_heads, head_dim, page_size, window, stride)
