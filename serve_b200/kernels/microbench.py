@@ -8,6 +8,7 @@
     python -m serve_b200.kernels.microbench step --preset llama-3.2-3b --layers 8 --batches 1,8,32 --context 2048 --tokens 2048
     python -m serve_b200.kernels.microbench layer_run --preset llama-3.2-1b --batches 8,1 --context 2048
     python -m serve_b200.kernels.microbench marginal --preset llama-3.2-1b --batches 8,1 --context 2048
+    python -m serve_b200.kernels.microbench long_prompt --preset llama-3.2-1b --context 32768 --tokens 8192
 
 Each repetition uses another copy of the weights or of the cache (``--copies``), so that data comes from HBM and
 not from the L2 cache; with ``--graph`` the repetitions are captured in one CUDA graph, as decoding steps are.
@@ -203,6 +204,43 @@ def _marginal_times(a) -> int:
     return 0
 
 
+def _long_prompt(a) -> int:
+    """One prompt of --context tokens in portions of --tokens: the time of every portion as the cached part grows."""
+    import dataclasses
+
+    from ..config import EngineConfig, load_preset
+    from ..engine import Engine, StepEntry
+
+    full = load_preset(a.preset)
+    cfg = dataclasses.replace(full, num_hidden_layers=a.layers or full.num_hidden_layers)
+    total, chunk = a.context, a.tokens
+    ec = EngineConfig(dtype="bfloat16", page_size=a.page_size, num_pages=2 * (total // a.page_size + 8), max_slots=4,
+                      max_tokens_per_step=chunk, max_context=total, device=a.device)
+    with torch.inference_mode():
+        eng = Engine.from_config(cfg, seed=0, engine_config=ec)
+        toks = torch.randint(0, cfg.vocab_size, (total,), generator=torch.Generator().manual_seed(0)).tolist()
+        for rep in range(2):                     # the second pass is the one reported
+            events = []
+            for i in range(0, total, chunk):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                eng.step([StepEntry(f"r{rep}", toks[i:i + chunk], [])])
+                e1.record()
+                events.append((e0, e1))
+            torch.cuda.synchronize()
+            ms = [x.elapsed_time(y) for x, y in events]
+            eng.end(f"r{rep}")
+        eng.kernels.check_errors()
+    flops = 4.0 * cfg.head_dim * cfg.num_attention_heads * chunk * (total - chunk / 2) * cfg.num_hidden_layers
+    more = (ms[-1] - ms[0]) * 1e-3
+    print(f"{a.preset}, {cfg.num_hidden_layers} layers: {total} tokens in portions of {chunk}: {sum(ms):.1f} ms = "
+          f"{total / sum(ms):.0f} k tokens/s; portions (ms): " + " ".join(f"{m:.1f}" for m in ms))
+    if more > 0:
+        print(f"attention of the last portion over the cached part: {flops / 1e12:.1f} TFLOP in {more * 1e3:.1f} ms more than the "
+              f"first portion = {flops / more / 1e12:.0f} TFLOP/s")
+    return 0
+
+
 def _layer_run_phases(a) -> int:
     """The persistent all-layers kernel (csrc/decode_stack.cu) on decoding steps of a preset's shape: what block 0's clock
     says after every phase and every barrier of three of the layers."""
@@ -252,7 +290,7 @@ def _layer_run_phases(a) -> int:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m serve_b200.kernels.microbench")
-    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention", "step", "layer_run", "marginal"])
+    ap.add_argument("kernel", choices=["linear", "gate_up", "qkv_rope", "decode_attention", "prefill_attention", "step", "layer_run", "marginal", "long_prompt"])
     ap.add_argument("--preset", default="llama-3.2-1b", help="step: the shape")
     ap.add_argument("--layers", type=int, default=None, help="step: fewer layers than the preset has")
     ap.add_argument("--batches", default="1,8,32", help="step: decoding batch sizes, comma separated")
@@ -281,6 +319,8 @@ def main(argv=None) -> int:
         return _layer_run_phases(a)
     if a.kernel == "marginal":
         return _marginal_times(a)
+    if a.kernel == "long_prompt":
+        return _long_prompt(a)
     from .cuda import load_kernels
 
     dev = a.device
