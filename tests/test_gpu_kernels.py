@@ -396,12 +396,14 @@ def test_attention_tensor_cores_against_plain_arithmetic(K, case):
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page,rows,max_q", [(32, 8, 64, 64, 150, 1), (16, 4, 128, 16, 300, 1), (24, 2, 64, 32, 520, 1),
-                                                               (8, 8, 64, 64, 140, 2), (12, 4, 32, 8, 260, 3), (32, 8, 64, 64, 100, 1)])
+                                                               (8, 8, 64, 64, 140, 2), (12, 4, 32, 8, 260, 3), (32, 8, 64, 64, 100, 1),
+                                                               (32, 8, 64, 64, 60, 1), (16, 8, 128, 16, 45, 2), (6, 2, 256, 32, 170, 1)])
 def test_decode_attention_for_a_crowd_of_short_requests(K, heads, kv_heads, d, page, rows, max_q):
-    """A thousand and more (request, kv head) pairs in one step (768 and more when no sequence is longer than 1,024
-    tokens) run one warp per pair. Short sequences of very different lengths, one to three new tokens each, groups of
-    1, 3, 4 and 12 query heads; unwritten cache rows hold NaN."""
-    assert rows * kv_heads >= 768
+    """Hundreds to thousands of (request, kv head) pairs in one step: blocks of one warp (a thousand and more pairs of
+    short sequences, or when two-warp blocks would leave a thin last round) or of two warps (more pairs than four-warp
+    blocks hold at once). Short sequences of very different lengths, one to three new tokens each, groups of 1 to 12
+    query heads; unwritten cache rows hold NaN."""
+    assert rows * kv_heads >= 300
     g = torch.Generator().manual_seed(rows)
     q_lens = torch.randint(1, max_q + 1, (rows,), generator=g).tolist()
     kv_lens = [q + int(x) for q, x in zip(q_lens, torch.randint(0, 330, (rows,), generator=g).tolist())]
