@@ -242,11 +242,29 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) attention_tc_kernel(cons
       mbar_expect_tx(&q_full, (unsigned)(tok_per_tile * G * D * 2));
 #pragma unroll
       for (int a = 0; a < KA; ++a) tma_load_4d(Qs + (size_t)a * BM * 128, &map_q, &q_full, a * 64, 0, hk, q0 + tok0);
-      const int pages_per_tile = BN / p.ps;
+      const bool big_pages = p.ps > BN;                  // a page holds several tiles (a multiple of BN keys)
+      const int pages_per_tile = big_pages ? 0 : BN / p.ps;
+      int big_blk = 0, big_at = 0;                        // big pages: the tile's page, and where in it the tile starts
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % NS;
         if (!mbar_wait(&kv_empty[s], ((j / NS) & 1) ^ 1)) { failed = true; break; }
         const int kt = j * BN, blk0 = j * pages_per_tile;   // pages tile the stage: no division in this thread's loop
+        if (big_pages) {
+          const bool there = kt < hi && big_blk < p.bt_width;
+          mbar_expect_tx(&kv_full[s], there ? (unsigned)(BN * D * 2 * 2) : 0u);
+          if (there) {
+            const int page = bt[big_blk];
+#pragma unroll
+            for (int a = 0; a < KA; ++a) {
+              const size_t off = (size_t)s * KV_BYTES + (size_t)a * BN * 128;
+              tma_load_4d(Ks + off, &map_k, &kv_full[s], a * 64, big_at, hk, page);
+              tma_load_4d(Vs + off, &map_v, &kv_full[s], a * 64, big_at, hk, page);
+            }
+          }
+          big_at += BN;
+          if (big_at == p.ps) { big_at = 0; ++big_blk; }
+          continue;
+        }
         int n_pages = 0;
         for (int i = 0; i < pages_per_tile; ++i)
           if (kt + i * p.ps < hi && blk0 + i < p.bt_width) ++n_pages;
@@ -459,7 +477,8 @@ SB_EXPORT int sb_attention_tc_supports(int H, int Hkv, int ps, int window, int q
   if (H <= 0 || Hkv <= 0 || H % Hkv) return 0;
   const int G = H / Hkv;
   if (G > 128) return 0;                                // a tile holds whole tokens: 128 / G of them (rows beyond stay unused)
-  if (ps < 8 || ps > BN || (BN % ps)) return 0;         // pages tile a stage of keys, in whole swizzle atoms
+  if (ps < 8) return 0;
+  if (ps <= BN ? (BN % ps) != 0 : ((ps % BN) != 0 || ps > 256)) return 0;   // pages tile a stage of keys (in whole swizzle atoms), or stages tile a page
   if (window > 0) return 0;
   if (q_stride % 8) return 0;
   return 1;
@@ -487,7 +506,7 @@ SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const
   {
     const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, (cuuint64_t)num_pages};
     const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)ps * D * 2, (cuuint64_t)Hkv * ps * D * 2};
-    const cuuint32_t box[4] = {64, (cuuint32_t)ps, 1, 1};
+    const cuuint32_t box[4] = {64, (cuuint32_t)(ps < BN ? ps : BN), 1, 1};
     int rc = encode4(&map_k, kc, dims, strides, box);
     if (rc) return rc;
     rc = encode4(&map_v, vc, dims, strides, box);

@@ -687,6 +687,8 @@ TC_ATT_CASES = [
     (10, 2, 32, [129, 90], [129, 500]),                    # group of 5
     (12, 1, 16, [70], [333]),                              # group of 12: ten tokens to a tile
     (100, 1, 64, [40], [40]),                              # group of 100: one token to a tile
+    (32, 8, 128, [300, 1, 70], [300, 700, 500]),           # pages of two key tiles
+    (6, 2, 256, [513, 40], [513, 1000]),                   # pages of four key tiles, sequences that end inside one
 ]
 
 
