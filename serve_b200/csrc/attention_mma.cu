@@ -416,6 +416,26 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
     }
     return;
   }
+  if (DKW == 32 && p.ps == 16) {
+    // pages of 16 tokens under sub-tiles of 32 keys: two pages, looked up once each; which of the two a copy belongs
+    // to is known when the loop is unrolled (row = (lane + 32 i) / CHUNKS)
+    const int blk = k0 >> 4;
+    const int page_a = blk < p.bt_width ? bt[blk - bt_first] : -1, page_b = blk + 1 < p.bt_width ? bt[blk + 1 - bt_first] : -1;
+    const bool ok_a = page_a >= 0 && page_a < p.num_pages, ok_b = page_b >= 0 && page_b < p.num_pages;
+    const size_t base_a = ((size_t)(ok_a ? page_a : 0) * p.Hkv + hk) * 16 * D, base_b = ((size_t)(ok_b ? page_b : 0) * p.Hkv + hk) * 16 * D;
+    const bool inner = k0 >= lo && k0 + DKW <= hi;
+#pragma unroll
+    for (int i = 0; i < DCOPIES; ++i) {
+      const int c = lane + 32 * i;
+      const int row = c / CHUNKS, ch = c - row * CHUNKS;
+      const bool second = row >= 16;
+      const bool ok = (second ? ok_b : ok_a) && (inner || (k0 + row >= lo && k0 + row < hi));
+      const size_t off = (second ? base_b : base_a) + (size_t)(row & 15) * D + ch * 8;
+      cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
+      cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < DCOPIES; ++i) {
     const int c = lane + 32 * i;
